@@ -7,7 +7,8 @@ The reference has one implicit group: a K and a V tensor ``[num_blocks, n_kv_hea
 block_size, head_size]`` per layer and one table per sequence (src/runtime/
 kv_cache_manager.cpp:63-81, include/photon/runtime/block_table.hpp:44-171).  The page
 layout here is the same; the pools of one group's entries live in one tensor
-``[entry, K|V, page, kv_head, slot, head_dim]``.
+``[entry, K|V, page, kv_head, slot, head_dim]`` (a group whose spec has no value rows keeps
+the K plane alone).
 """
 from __future__ import annotations
 
@@ -33,12 +34,12 @@ class CacheGroup:
         self.tables: Dict[object, List[int]] = {}
         self.kv: Optional[torch.Tensor] = None
         if device is not None:
-            self.kv = torch.zeros((len(entries), 2, num_pages, spec.n_kv_heads, page_size, spec.head_dim),
+            self.kv = torch.zeros((len(entries), spec.planes, num_pages, spec.n_kv_heads, page_size, spec.head_dim),
                                   dtype=dtype, device=device)
 
     # ------------------------------------------------------------------ sizes
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.entries) * 2 * self.spec.n_kv_heads * self.spec.head_dim * element_size
+        return len(self.entries) * self.spec.planes * self.spec.n_kv_heads * self.spec.head_dim * element_size
 
     def first_visible(self, length: int) -> int:
         """First key that a token at position ``length`` (the next one) can still see."""

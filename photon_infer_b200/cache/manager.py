@@ -194,7 +194,7 @@ class CacheManager:
                 lc.shared = self.entry_shared[i]
                 if self.groups[g].kv is not None:
                     lc.k = self.groups[g].kv[slot, 0]
-                    lc.v = self.groups[g].kv[slot, 1]
+                    lc.v = self.groups[g].kv[slot, 1] if self.groups[g].spec.values else None
             lc.state = self.states.tensors.get(i)
             out.append(lc)
         return out

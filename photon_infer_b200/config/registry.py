@@ -45,16 +45,24 @@ def registered_architectures():
     return sorted(_ARCHITECTURES)
 
 
+def architecture_name(d: Dict[str, Any]) -> str:
+    """The model class a configuration asks for: ``architectures[0]`` (a list of names) or ``architecture`` (one name)."""
+    archs = d.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if isinstance(d.get("architecture"), str):
+        return d["architecture"]
+    raise PhotonError(ErrorCode.INVALID_CONFIG,
+                      "config.json: key 'architectures' (a non-empty list of names) or 'architecture' (a name) is needed")
+
+
 def load_config(path: str):
     """Read ``config.json`` and return ``(architecture, typed config)``."""
     d = read_config_json(path)
-    archs = d.get("architectures")
-    if not isinstance(archs, list) or not archs:
-        raise PhotonError(ErrorCode.INVALID_CONFIG, "config.json: key 'architectures' must be a non-empty list")
-    arch = get_architecture(archs[0])
+    arch = get_architecture(architecture_name(d))
     return arch, arch.config_class.from_dict(d)
 
 
 def _ensure_builtin() -> None:
     # importing the model module registers it
-    from ..models import llama  # noqa: F401
+    from ..models import finelix, llama  # noqa: F401

@@ -15,6 +15,12 @@
 // The tile grid starts at key 0 (at a multiple of 32 at or below the window's first
 // key), so the order of every sum depends only on the token's position, never on how
 // the request was cut into steps or on what else is in the batch.
+//
+// Two generalisations serve mixers whose keys and values are not two tensors of one head size.  The value of
+// a key is `dv` numbers wide (dv <= d); with v_cache == k_cache the value is the first dv numbers of the key's
+// own row (attention over a cached latent: the latent is key and value at once, the rest of the row is a
+// rotated key part).  And the query heads that share a key/value head are cut into chunks of `hb` heads per
+// block, so that any number of query heads may share one key/value head.
 #include "common.cuh"
 #include <math.h>
 
@@ -27,20 +33,25 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        const int* __restrict__ block_table, int max_pages,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
-                       int n_q, int n_kv, int d, int page_size, int num_pages, int window, float scale,
-                       int* err) {
+                       int n_q, int n_kv, int d, int dv, int hb, int page_size, int num_pages, int window,
+                       float scale, int* err) {
   extern __shared__ __align__(16) float smem[];
-  const int t = blockIdx.x, g = blockIdx.y;
-  const int G = n_q / n_kv;
+  const int chunks = (n_q / n_kv + hb - 1) / hb;
+  const int t = blockIdx.x, g = blockIdx.y / chunks;
+  const int h0 = g * (n_q / n_kv) + (blockIdx.y % chunks) * hb;            // first query head of this block
+  const int G = min(hb, (g + 1) * (n_q / n_kv) - h0);                      // query heads of this block
+  const bool shared_kv = (const void*)v_cache == (const void*)k_cache;    // values are the head of the key rows
+  const int vld = shared_kv ? d + 1 : dv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* qs = smem;                          // G * d
-  float* ks = qs + G * d;                    // TILE * (d + 1)
-  float* vs = ks + ATT_TILE * (d + 1);       // TILE * d
-  float* sc = vs + ATT_TILE * d;             // G * TILE
-  float* mrun = sc + G * ATT_TILE;           // G
-  float* lsum = mrun + G;                    // G
-  float* corr = lsum + G;                    // G
-  long long* kbase = (long long*)(corr + G + ((G & 1) ? 1 : 0));   // TILE (8-byte aligned)
+  float* ks = qs + hb * d;                   // TILE * (d + 1)
+  float* vs = ks + ATT_TILE * (d + 1);       // TILE * dv (not used when the values lie in the key rows)
+  float* sc = vs + (shared_kv ? 0 : ATT_TILE * dv);   // hb * TILE
+  float* mrun = sc + hb * ATT_TILE;          // hb
+  float* lsum = mrun + hb;                   // hb
+  float* corr = lsum + hb;                   // hb
+  long long* kbase = (long long*)(corr + hb + ((hb & 1) ? 1 : 0));   // TILE (8-byte aligned)
+  if (shared_kv) vs = ks;
 
   const int p = positions[t];
   const int seq = token_seq[t];
@@ -49,7 +60,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 
   for (int i = tid; i < G * d; i += ATT_THREADS) {
     const int h = i / d, j = i - h * d;
-    qs[i] = to_f32(q[(size_t)t * q_stride + (size_t)(g * G + h) * d + j]);
+    qs[i] = to_f32(q[(size_t)t * q_stride + (size_t)(h0 + h) * d + j]);
   }
   for (int h = tid; h < G; h += ATT_THREADS) { mrun[h] = -INFINITY; lsum[h] = 0.f; corr[h] = 0.f; }
   float acc[PPT];
@@ -76,7 +87,13 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
       const int key = i / d, j = i - key * d;
       const long long base = kbase[key];
       ks[key * (d + 1) + j] = base >= 0 ? to_f32(k_cache[base + j]) : 0.f;
-      vs[key * d + j] = base >= 0 ? to_f32(v_cache[base + j]) : 0.f;
+    }
+    if (!shared_kv) {
+      for (int i = tid; i < ATT_TILE * dv; i += ATT_THREADS) {
+        const int key = i / dv, j = i - key * dv;
+        const long long base = kbase[key];
+        vs[key * dv + j] = base >= 0 ? to_f32(v_cache[base / d * dv + j]) : 0.f;
+      }
     }
     __syncthreads();
     // scores
@@ -111,12 +128,12 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 #pragma unroll
     for (int n = 0; n < PPT; ++n) {
       const int i = tid + n * ATT_THREADS;
-      if (i < G * d) {
-        const int h = i / d, j = i - h * d;
+      if (i < G * dv) {
+        const int h = i / dv, j = i - h * dv;
         float a = acc[n] * corr[h];
         const float* pr = sc + h * ATT_TILE;
 #pragma unroll 8
-        for (int key = 0; key < ATT_TILE; ++key) a += pr[key] * vs[key * d + j];
+        for (int key = 0; key < ATT_TILE; ++key) a += pr[key] * vs[key * vld + j];
         acc[n] = a;
       }
     }
@@ -125,10 +142,10 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 #pragma unroll
   for (int n = 0; n < PPT; ++n) {
     const int i = tid + n * ATT_THREADS;
-    if (i < G * d) {
-      const int h = i / d, j = i - h * d;
+    if (i < G * dv) {
+      const int h = i / dv, j = i - h * dv;
       const float l = lsum[h];
-      out[(size_t)t * out_stride + (size_t)(g * G + h) * d + j] = from_f32<T>(l > 0.f ? acc[n] / l : 0.f);
+      out[(size_t)t * out_stride + (size_t)(h0 + h) * dv + j] = from_f32<T>(l > 0.f ? acc[n] / l : 0.f);
     }
   }
 }
@@ -136,10 +153,11 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 template <typename T, int PPT>
 static int attention_launch(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                             const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
-                            const int* positions, int T_, int n_q, int n_kv, int d, int page_size,
+                            const int* positions, int T_, int n_q, int n_kv, int d, int dv, int hb, int page_size,
                             int num_pages, int window, float scale, int* err, cudaStream_t stream) {
-  const int G = n_q / n_kv;
-  const size_t floats = (size_t)G * d + ATT_TILE * (d + 1) + ATT_TILE * d + (size_t)G * ATT_TILE + 3 * G + 1;
+  const int G = hb;
+  const size_t floats = (size_t)G * d + ATT_TILE * (d + 1) + (v_cache == k_cache ? 0 : ATT_TILE * dv) +
+                        (size_t)G * ATT_TILE + 3 * G + 1;
   const size_t smem = floats * sizeof(float) + ATT_TILE * sizeof(long long) + 8;
   if (smem > 220 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
@@ -147,10 +165,10 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(T_, n_kv);
+  dim3 grid(T_, n_kv * ((n_q / n_kv + hb - 1) / hb));
   paged_attention_kernel<T, PPT><<<grid, ATT_THREADS, smem, stream>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_table,
-      max_pages, token_seq, positions, n_q, n_kv, d, page_size, num_pages, window, scale, err);
+      max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, err);
   return launch_status();
 }
 
@@ -164,18 +182,24 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
   return PHOTON_ERR_UNSUPPORTED;
 
 #define ATT_ARGS q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, token_seq, \
-                 positions, T_, n_q, n_kv, d, page_size, num_pages, window, scale, err, stream
+                 positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, err, stream
 
-// window <= 0: all keys.  Strides in elements.  The cache holds [num_pages][n_kv][page_size][d].
+// window <= 0: all keys.  Strides in elements.  The key cache holds [num_pages][n_kv][page_size][d], the value
+// cache [num_pages][n_kv][page_size][dv]; v_cache == k_cache (dv <= d): a key's value is the head of its row.
+// out [T][n_q * dv].  A block runs up to 4096 / max(d, dv) of the query heads that share a key/value head.
 PHOTON_API int photon_paged_attention(const void* q, long q_stride, void* out, long out_stride, int dtype,
                                       const void* k_cache, const void* v_cache, const int* block_table,
                                       int max_pages, const int* token_seq, const int* positions, int T_,
-                                      int n_q, int n_kv, int d, int page_size, int num_pages, int window,
+                                      int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window,
                                       float scale, int* err, cudaStream_t stream) {
   if (T_ <= 0) return 0;
-  if (n_kv <= 0 || n_q % n_kv || d <= 0 || page_size <= 0) return PHOTON_ERR_ARGUMENT;
-  const int G = n_q / n_kv;
-  const int ppt = (G * d + ATT_THREADS - 1) / ATT_THREADS;
+  if (n_kv <= 0 || n_q % n_kv || d <= 0 || dv <= 0 || page_size <= 0) return PHOTON_ERR_ARGUMENT;
+  if (v_cache == k_cache && dv > d) return PHOTON_ERR_ARGUMENT;
+  if (d > 4096 || dv > 4096) return PHOTON_ERR_UNSUPPORTED;
+  int hb = 4096 / (d > dv ? d : dv);
+  if (hb > n_q / n_kv) hb = n_q / n_kv;
+  if ((long)n_kv * ((n_q / n_kv + hb - 1) / hb) > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const int ppt = (hb * dv + ATT_THREADS - 1) / ATT_THREADS;
   if (n_kv > 65535) return PHOTON_ERR_UNSUPPORTED;
   if (dtype == PHOTON_BF16) { ATT_DISPATCH(bf16) }
   ATT_DISPATCH(float)

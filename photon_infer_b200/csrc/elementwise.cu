@@ -59,8 +59,8 @@ template <> struct Quad<bf16> {
 
 // VEC: rows are read and written four elements at a time (H a multiple of 4, aligned pointers).
 template <typename TD, typename TO, bool VEC>
-__global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          // written by earlier kernels that may
-                                   const void* __restrict__ w, int w_bf16,    // still run when this one starts: no
+__global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* residual,   // written by earlier kernels that
+                                   const void* __restrict__ w, int w_bf16,    // may still run when this one starts: no
                                    TO* out, const int* rows, int H, float eps) {  // read-only path for them
   __shared__ float red[32];
   extern __shared__ __align__(16) float stash[];               // H floats: the summed row
@@ -68,6 +68,7 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* res = residual + (size_t)r * H;
   const TD* d = delta ? delta + (size_t)r * H : nullptr;
+  const TD* d2 = (delta && delta2) ? delta2 + (size_t)r * H : nullptr;   // a second sublayer's output (parallel blocks)
   float ss = 0.f;
   if (VEC) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
@@ -75,6 +76,12 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
       Quad<float>::load(res + i, v);
       if (d) {
         Quad<TD>::load(d + i, dv);
+        if (d2) {
+          float dw[4];
+          Quad<TD>::load(d2 + i, dw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dv[e] += dw[e];
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[e] += dv[e];
       }
@@ -85,7 +92,7 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       float v = res[i];
-      if (d) v += to_f32(d[i]);
+      if (d) v += d2 ? to_f32(d[i]) + to_f32(d2[i]) : to_f32(d[i]);
       stash[i] = v;
       ss += v * v;
     }
@@ -114,11 +121,11 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
 }
 
 template <typename TD, typename TO>
-static int add_rmsnorm_launch(const void* delta, float* residual, const void* w, int w_bf16, void* out,
+static int add_rmsnorm_launch(const void* delta, const void* delta2, float* residual, const void* w, int w_bf16, void* out,
                               const int* rows, int n, int H, float eps, cudaStream_t stream) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
-  const bool vec = (H % 4 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
+  const bool vec = (H % 4 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)delta2 % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
                    ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (smem > 48 * 1024) {
     cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
@@ -131,32 +138,39 @@ static int add_rmsnorm_launch(const void* delta, float* residual, const void* w,
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
   if (vec)
     return launch_pdl(add_rmsnorm_kernel<TD, TO, true>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                      residual, w, w_bf16, (TO*)out, rows, H, eps);
+                      (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps);
   return launch_pdl(add_rmsnorm_kernel<TD, TO, false>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                    residual, w, w_bf16, (TO*)out, rows, H, eps);
+                    (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps);
 }
 
-// delta may be null (plain norm).  delta_dtype / out_dtype: PHOTON_F32 or PHOTON_BF16.
-PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, float* residual, const void* w,
+// delta may be null (plain norm); delta2 (same type as delta, may be null) is added as well: the sum of the two is
+// formed first, in 32-bit, and then added to the residual.  delta_dtype / out_dtype: PHOTON_F32 or PHOTON_BF16.
+PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                                   int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
                                   float eps, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int wb = (w_dtype == PHOTON_BF16);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<bf16, bf16>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<bf16, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<float, float>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<float, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
   if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
-    return add_rmsnorm_launch<float, bf16>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<float, bf16>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
   if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_F32)
-    return add_rmsnorm_launch<bf16, float>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+    return add_rmsnorm_launch<bf16, float>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream);
   return PHOTON_ERR_ARGUMENT;
 }
 
-// ---------------------------------------------------------------- SwiGLU
-// gate_up [T, 2*I]: columns [0, I) are the gate, [I, 2I) the up projection.  out [T, I].
+// ---------------------------------------------------------------- gated activation (SwiGLU, GeGLU)
+// gate_up [T, 2*I]: columns [0, I) are the gate, [I, 2I) the up projection.  out [T, I] = act(gate) * up.
+// act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == PHOTON_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total, int act) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
@@ -164,14 +178,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const int i = (int)(idx - t * I);
     const float g = to_f32(gate_up[t * 2 * I + i]);
     const float u = to_f32(gate_up[t * 2 * I + I + i]);
-    const float s = g / (1.0f + expf(-g));
-    out[idx] = from_f32<T>(s * u);
+    out[idx] = from_f32<T>(glu_act(g, act) * u);
   }
 }
 
 // The same, 16 bytes per load: I a multiple of the elements in 16 bytes, aligned pointers.
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total_vecs) {
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total_vecs, int act) {
   constexpr int N = 16 / sizeof(T);
   const int per_row = I / N;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -188,13 +201,14 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__
 #pragma unroll
     for (int e = 0; e < N; ++e) {
       const float g = to_f32(gp[e]);
-      op[e] = from_f32<T>(g / (1.0f + expf(-g)) * to_f32(up[e]));
+      op[e] = from_f32<T>(glu_act(g, act) * to_f32(up[e]));
     }
     *reinterpret_cast<uint4*>(out + t * I + i) = ov;
   }
 }
 
-PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+PHOTON_API int photon_glu(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
+  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH) return PHOTON_ERR_ARGUMENT;
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
@@ -205,11 +219,68 @@ PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, i
   const size_t cap = (size_t)photon_sm_count() * 16;
   if (blocks > cap) blocks = cap;
   if (dtype == PHOTON_BF16) {
-    if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, work);
-    else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, work, act);
+    else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total, act);
   } else {
-    if (vec) swiglu_vec_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, work);
-    else swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+    if (vec) swiglu_vec_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, work, act);
+    else swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, act);
   }
+  return launch_status();
+}
+
+PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+  return photon_glu(gate_up, out, dtype, T, I, PHOTON_ACT_SILU, stream);
+}
+
+// ---------------------------------------------------------------- the stream joined with a second one
+// out [T, 2H] (TO) = [residual + delta + delta2 ; other]: the input of a product that mixes the running stream
+// with another stream of the same width (the embedding output, for a block of layers that is entered again).
+// delta and delta2 may be null.  The sum is formed in 32-bit and rounded once.
+template <typename TD, typename TO>
+__global__ void stream_concat_kernel(const float* residual, const TD* delta, const TD* delta2, const float* other,
+                                     TO* out, int H) {
+  const size_t r = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = residual[r * H + i];
+    if (delta) v += delta2 ? to_f32(delta[r * H + i]) + to_f32(delta2[r * H + i]) : to_f32(delta[r * H + i]);
+    out[r * 2 * H + i] = from_f32<TO>(v);
+    out[r * 2 * H + H + i] = from_f32<TO>(other[r * H + i]);
+  }
+}
+
+PHOTON_API int photon_stream_concat(const float* residual, const void* delta, const void* delta2, int delta_dtype,
+                                    const float* other, void* out, int out_dtype, int T, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
+    stream_concat_kernel<bf16, bf16><<<T, threads, 0, stream>>>(residual, (const bf16*)delta, (const bf16*)delta2, other, (bf16*)out, H);
+  else if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
+    stream_concat_kernel<float, float><<<T, threads, 0, stream>>>(residual, (const float*)delta, (const float*)delta2, other, (float*)out, H);
+  else if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
+    stream_concat_kernel<float, bf16><<<T, threads, 0, stream>>>(residual, (const float*)delta, (const float*)delta2, other, (bf16*)out, H);
+  else
+    return PHOTON_ERR_ARGUMENT;
+  return launch_status();
+}
+
+// x [T, H] (float, in place) = x * scale + bias (bias [H] may be null; stored as float or bfloat16).
+__global__ void scale_bias_rows_kernel(float* x, float scale, const void* bias, int bias_bf16, int H, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    float v = x[idx] * scale;
+    if (bias) v += load_w(bias, bias_bf16, idx % H);
+    x[idx] = v;
+  }
+}
+
+PHOTON_API int photon_scale_bias_rows(float* x, float scale, const void* bias, int bias_dtype, int T, int H,
+                                      cudaStream_t stream) {
+  const size_t total = (size_t)T * H;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = (size_t)photon_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  scale_bias_rows_kernel<<<(int)blocks, 256, 0, stream>>>(x, scale, bias, bias_dtype == PHOTON_BF16, H, total);
   return launch_status();
 }

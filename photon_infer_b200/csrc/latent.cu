@@ -1,0 +1,209 @@
+// Kernels of attention over a cached latent: every token stores ONE row [c ; k_r] of kv_rank + rot numbers,
+// the normed latent c and a rotated key part k_r shared by all heads.  A head's unrotated key is W_uk c and
+// its value W_uv c; neither is ever formed.  With q_abs = W_uk^T q_unrotated the score of a head is
+// (q_abs . c + q_r . k_r) * scale, the weighted sum of the latents is taken per head, and W_uv is applied to
+// that sum.  The attention itself is photon_paged_attention with one key/value head whose values are the head
+// of the key rows; this file holds what comes before and after it:
+//
+//   photon_latent_prep      one pass over the fused down-projection row of a token: RMS norm of the query
+//                           latent, RMS norm of the key/value latent, rotation of the shared key part, and the
+//                           row's write into the paged cache;
+//   photon_latent_q_rope    the rotated part of every head's query, copied behind the absorbed part;
+//   photon_head_linear      out[t, h, :] = W[h] x[t, h, :] for all heads in one launch (the absorption of W_uk
+//                           into the queries and the application of W_uv to the attention result).
+//
+// Rotation: the first rot_dims numbers of the rotated part, feature i paired with i + rot_dims / 2, angle
+// position * inv_freq[i] in 32-bit; features beyond rot_dims pass unchanged.  All arithmetic is 32-bit.
+#include "common.cuh"
+#include <math.h>
+
+// ---------------------------------------------------------------- norms, rotation, cache write
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ down, long down_stride, int q_rank, int kv_rank, int rot,
+                                   int rot_dims, const void* __restrict__ qw, int qw_bf16,
+                                   const void* __restrict__ kw, int kw_bf16, float eps,
+                                   const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                   const int* __restrict__ slot_mapping, T* __restrict__ cq, long cq_stride,
+                                   T* __restrict__ cache, long num_slots, int* err) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const T* row = down + (size_t)t * down_stride;
+  // query latent
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f32(row[i]); ss += v * v; }
+  ss = block_sum(ss, red);
+  const float qinv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+    cq[(size_t)t * cq_stride + i] = from_f32<T>(to_f32(row[i]) * qinv * load_w(qw, qw_bf16, i));
+  // key/value latent
+  const T* kv = row + q_rank;
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_f32(kv[i]); s2 += v * v; }
+  s2 = block_sum(s2, red);
+  const float kinv = 1.0f / sqrtf(s2 / (float)kv_rank + eps);
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;                                 // a padding row: nothing is stored
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t, slot, (int)num_slots);
+    return;
+  }
+  T* dst = cache + (size_t)slot * (kv_rank + rot);
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
+    dst[i] = from_f32<T>(to_f32(kv[i]) * kinv * load_w(kw, kw_bf16, i));
+  const T* kr = kv + kv_rank;
+  const int half = rot_dims / 2;
+  const float p = (float)positions[t];
+  for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+    float y;
+    if (i < half) {
+      float sn, cs;
+      sincosf(p * inv_freq[i], &sn, &cs);
+      y = to_f32(kr[i]) * cs - to_f32(kr[i + half]) * sn;
+    } else if (i < rot_dims) {
+      float sn, cs;
+      sincosf(p * inv_freq[i - half], &sn, &cs);
+      y = to_f32(kr[i]) * cs + to_f32(kr[i - half]) * sn;
+    } else {
+      y = to_f32(kr[i]);
+    }
+    dst[kv_rank + i] = from_f32<T>(y);
+  }
+}
+
+// down [T][q_rank + kv_rank + rot] (row stride in elements): the fused down-projections of a token.
+// cq [T][q_rank]: the normed query latent.  cache: [num_slots][kv_rank + rot], the pages of one layer.
+PHOTON_API int photon_latent_prep(const void* down, long down_stride, int dtype, int q_rank, int kv_rank, int rot,
+                                  int rot_dims, const void* q_norm_w, int q_norm_dtype, const void* kv_norm_w,
+                                  int kv_norm_dtype, float eps, const int* positions, const float* inv_freq,
+                                  const int* slot_mapping, void* cq, long cq_stride, void* cache, long num_slots,
+                                  int T_, int* err, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (q_rank <= 0 || kv_rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return PHOTON_ERR_ARGUMENT;
+  const int threads = 128;
+  if (dtype == PHOTON_BF16)
+    latent_prep_kernel<bf16><<<T_, threads, 0, stream>>>((const bf16*)down, down_stride, q_rank, kv_rank, rot, rot_dims,
+        q_norm_w, q_norm_dtype == PHOTON_BF16, kv_norm_w, kv_norm_dtype == PHOTON_BF16, eps, positions, inv_freq,
+        slot_mapping, (bf16*)cq, cq_stride, (bf16*)cache, num_slots, err);
+  else
+    latent_prep_kernel<float><<<T_, threads, 0, stream>>>((const float*)down, down_stride, q_rank, kv_rank, rot, rot_dims,
+        q_norm_w, q_norm_dtype == PHOTON_BF16, kv_norm_w, kv_norm_dtype == PHOTON_BF16, eps, positions, inv_freq,
+        slot_mapping, (float*)cq, cq_stride, (float*)cache, num_slots, err);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- rotated query parts
+// q [T][heads][dim + rot] -> out [T][heads][out_head] at offset out_off: the last rot numbers of every head, rotated.
+template <typename T>
+__global__ void latent_q_rope_kernel(const T* __restrict__ q, long q_stride, int heads, int dim, int rot, int rot_dims,
+                                     const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                     T* __restrict__ out, long out_stride, int out_head, int out_off) {
+  const int t = blockIdx.x;
+  const float p = (float)positions[t];
+  const int half = rot_dims / 2;
+  for (int idx = threadIdx.x; idx < heads * rot; idx += blockDim.x) {
+    const int h = idx / rot, i = idx - h * rot;
+    const T* src = q + (size_t)t * q_stride + (size_t)h * (dim + rot) + dim;
+    float y;
+    if (i < half) {
+      float sn, cs;
+      sincosf(p * inv_freq[i], &sn, &cs);
+      y = to_f32(src[i]) * cs - to_f32(src[i + half]) * sn;
+    } else if (i < rot_dims) {
+      float sn, cs;
+      sincosf(p * inv_freq[i - half], &sn, &cs);
+      y = to_f32(src[i]) * cs + to_f32(src[i - half]) * sn;
+    } else {
+      y = to_f32(src[i]);
+    }
+    out[(size_t)t * out_stride + (size_t)h * out_head + out_off + i] = from_f32<T>(y);
+  }
+}
+
+PHOTON_API int photon_latent_q_rope(const void* q, long q_stride, int dtype, int heads, int dim, int rot, int rot_dims,
+                                    const int* positions, const float* inv_freq, void* out, long out_stride,
+                                    int out_head, int out_off, int T_, cudaStream_t stream) {
+  if (T_ <= 0 || rot <= 0) return 0;
+  if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1)) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_BF16)
+    latent_q_rope_kernel<bf16><<<T_, 128, 0, stream>>>((const bf16*)q, q_stride, heads, dim, rot, rot_dims, positions,
+                                                      inv_freq, (bf16*)out, out_stride, out_head, out_off);
+  else
+    latent_q_rope_kernel<float><<<T_, 128, 0, stream>>>((const float*)q, q_stride, heads, dim, rot, rot_dims, positions,
+                                                       inv_freq, (float*)out, out_stride, out_head, out_off);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- one product per head
+// out[t, h, n] = sum_k x[t, h, k] * W[h, n, k], accumulated in 32-bit as one chain of K fused multiply-adds in
+// ascending k (a row's result depends on nothing but the row).  Tiles of 64 tokens x 64 features per block.
+#define HL_BM 64
+#define HL_BN 64
+#define HL_BK 16
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_linear_kernel(const T* __restrict__ x, long x_row, long x_head, const T* __restrict__ W, T* __restrict__ out,
+                   long o_row, long o_head, int M, int N, int K) {
+  __shared__ float As[HL_BK][HL_BM + 4];
+  __shared__ float Ws[HL_BK][HL_BN + 4];
+  const int h = blockIdx.z;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * HL_BM, n0 = blockIdx.x * HL_BN;
+  const T* A = x + (size_t)h * x_head;
+  const T* Wh = W + (size_t)h * N * K;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HL_BK) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int idx = tid + r * 256;
+      const int row = idx >> 4, kk = idx & 15;
+      const int gm = m0 + row, gn = n0 + row, gk = k0 + kk;
+      As[kk][row] = (gm < M && gk < K) ? to_f32(A[(size_t)gm * x_row + gk]) : 0.f;
+      Ws[kk][row] = (gn < N && gk < K) ? to_f32(Wh[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HL_BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) out[(size_t)gm * o_row + (size_t)h * o_head + gn] = from_f32<T>(acc[i][j]);
+    }
+  }
+}
+
+// x [M][heads][K] and out [M][heads][N] with row and head strides in elements; W [heads][N][K] contiguous.
+PHOTON_API int photon_head_linear(const void* x, long x_row, long x_head, const void* W, void* out, long o_row,
+                                  long o_head, int dtype, int M, int heads, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || heads <= 0 || N <= 0) return 0;
+  if (K <= 0) return PHOTON_ERR_ARGUMENT;
+  dim3 grid((N + HL_BN - 1) / HL_BN, (M + HL_BM - 1) / HL_BM, heads);
+  if (grid.y > 65535 || grid.z > 65535) return PHOTON_ERR_UNSUPPORTED;
+  if (dtype == PHOTON_BF16)
+    head_linear_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, x_row, x_head, (const bf16*)W, (bf16*)out, o_row,
+                                                      o_head, M, N, K);
+  else
+    head_linear_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, x_row, x_head, (const float*)W, (float*)out,
+                                                       o_row, o_head, M, N, K);
+  return launch_status();
+}

@@ -1,0 +1,269 @@
+// Routed experts: a router picks `top` of E small gated feed-forward layers for every token.
+//
+//   photon_moe_route     logits z = W_r h + b in 32-bit, the `top` largest (the lower index wins a tie), weights =
+//                        softmax over the chosen logits only; counts the tokens of every expert;
+//   photon_moe_align     sorts the (token, choice) pairs by expert, stably, without the host: offsets of every
+//                        expert in the sorted order, the sorted list, every pair's place in it, and the list
+//                        of row tiles (expert, first row, rows) that the grouped products walk;
+//   photon_moe_gemm      grouped product over the sorted rows: each row tile multiplies with its expert's
+//                        matrix; rows of A are gathered through the sorted list (first product) or lie in
+//                        sorted order already (second product); optional gated activation in the epilogue;
+//   photon_moe_combine   out[t] = sum_j weight[t, j] * y[place(t, j)] (+ the shared expert's output), the sum in
+//                        32-bit in the order of j.
+//
+// Every output of a product is one chain of K fused multiply-adds in ascending k, accumulated in 32-bit, so a
+// token's result depends neither on the other tokens of the step nor on its place in the sorted order.
+#include "common.cuh"
+#include <math.h>
+
+#define MOE_BM 32          // rows of a tile of the grouped products
+
+// ---------------------------------------------------------------- router
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ Wr,
+                                 const void* __restrict__ bias, int bias_bf16, int H, int E, int top,
+                                 int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T_) {
+  extern __shared__ float logits[];                     // warps x E
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T_) return;
+  float* lg = logits + warp * E;
+  const T* x = h + (size_t)t * h_stride;
+  for (int e = 0; e < E; ++e) {
+    const T* w = Wr + (size_t)e * H;
+    float acc = 0.f;
+    for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(x[k]), to_f32(w[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) lg[e] = acc + (bias ? load_w(bias, bias_bf16, e) : 0.f);
+  }
+  __syncwarp();
+  if (lane == 0) {
+    float chosen_max = -INFINITY;
+    for (int j = 0; j < top; ++j) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; ++e) {
+        const float v = lg[e];
+        if (best < 0 || v > bv) { bv = v; best = e; }
+      }
+      ids[(size_t)t * top + j] = best;
+      weights[(size_t)t * top + j] = bv;
+      if (j == 0) chosen_max = bv;
+      lg[best] = -INFINITY;
+      atomicAdd(&counts[best], 1);
+    }
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const float p = expf(weights[(size_t)t * top + j] - chosen_max);
+      weights[(size_t)t * top + j] = p;
+      sum += p;
+    }
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= sum;
+  }
+}
+
+// h [T][H] (row stride in elements), Wr [E][H] of the same type, bias [E] (may be null).  ids, weights [T][top];
+// counts [E] is cleared first and then holds the number of (token, choice) pairs of every expert.
+PHOTON_API int photon_moe_route(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype,
+                                int T_, int H, int E, int top, int* ids, float* weights, int* counts,
+                                cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || H <= 0) return PHOTON_ERR_ARGUMENT;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  if (smem > 48 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  const int blocks = (T_ + warps - 1) / warps;
+  if (dtype == PHOTON_BF16)
+    moe_route_kernel<bf16><<<blocks, warps * 32, smem, stream>>>((const bf16*)h, h_stride, (const bf16*)Wr, bias,
+                                                                bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_);
+  else
+    moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>((const float*)h, h_stride, (const float*)Wr, bias,
+                                                                 bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- sort by expert
+// One block per expert e: its first row in the sorted order is the number of pairs of the experts before it, and
+// its pairs take the following places in the order in which they stand in `ids`.
+__global__ void moe_align_kernel(const int* __restrict__ ids, const int* __restrict__ counts, int n, int E,
+                                 int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ place,
+                                 int* __restrict__ tiles, int* __restrict__ num_tiles) {
+  __shared__ int warp_tot[32];
+  __shared__ int base_s;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  if (threadIdx.x == 0) {
+    int off = 0, tl = 0;
+    for (int i = 0; i < e; ++i) { off += counts[i]; tl += (counts[i] + MOE_BM - 1) / MOE_BM; }
+    base_s = off;
+    offsets[e] = off;
+    const int own = counts[e];
+    for (int i = 0; i * MOE_BM < own; ++i) {
+      tiles[3 * (tl + i)] = e;
+      tiles[3 * (tl + i) + 1] = off + i * MOE_BM;
+      tiles[3 * (tl + i) + 2] = min(MOE_BM, own - i * MOE_BM);
+    }
+    if (e == E - 1) { offsets[E] = off + own; *num_tiles = tl + (own + MOE_BM - 1) / MOE_BM; }
+  }
+  __syncthreads();
+  int running = base_s;
+  for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    const bool mine = i < n && ids[i] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    const int before = __popc(ballot & ((1u << lane) - 1u));
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int wbase = 0, total = 0;
+    for (int w = 0; w < nwarp; ++w) { if (w < warp) wbase += warp_tot[w]; total += warp_tot[w]; }
+    if (mine) { const int p = running + wbase + before; sorted[p] = i; place[i] = p; }
+    running += total;
+    __syncthreads();
+  }
+}
+
+// ids [n] (n = T * top), counts [E] -> offsets [E + 1], sorted [n] (pair index at each sorted row), place [n]
+// (sorted row of each pair), tiles [3 * max_tiles] (expert, first row, rows), num_tiles [1].
+// max_tiles >= n / MOE_BM + E always suffices.
+PHOTON_API int photon_moe_align(const int* ids, const int* counts, int n, int E, int* offsets, int* sorted, int* place,
+                                int* tiles, int* num_tiles, cudaStream_t stream) {
+  if (n <= 0 || E <= 0) return 0;
+  moe_align_kernel<<<E, 256, 0, stream>>>(ids, counts, n, E, offsets, sorted, place, tiles, num_tiles);
+  return launch_status();
+}
+
+PHOTON_API int photon_moe_tile_rows(void) { return MOE_BM; }
+
+// ---------------------------------------------------------------- grouped product
+#define MOE_BN 64
+#define MOE_BK 16
+
+__device__ __forceinline__ float moe_act(float g, int act) {
+  if (act == PHOTON_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+// GLU: W holds [gate rows; up rows] per expert (N = 2 * cols); the block computes the gate and the up column of
+// each of its output columns and stores act(gate) * up.
+template <typename T, typename TO, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ A, long lda, const int* __restrict__ gather, int gather_div,
+                const T* __restrict__ W, TO* __restrict__ out, long ldo, int N, int K,
+                const int* __restrict__ tiles, const int* __restrict__ num_tiles, int act) {
+  __shared__ float As[MOE_BK][MOE_BM + 4];
+  __shared__ float Ws[GLU ? 2 : 1][MOE_BK][MOE_BN + 4];
+  __shared__ int arow[MOE_BM];
+  const int tile = blockIdx.y;
+  if (tile >= *num_tiles) return;
+  const int e = tiles[3 * tile], r0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+  const int cols = GLU ? N / 2 : N;
+  const int n0 = blockIdx.x * MOE_BN;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;       // 16 x 16 threads: 2 rows x 4 columns each
+  const T* We = W + (size_t)e * N * K;
+  if (tid < MOE_BM) arow[tid] = tid < rows ? (gather ? gather[r0 + tid] / gather_div : r0 + tid) : -1;
+  __syncthreads();
+  float acc[GLU ? 2 : 1][2][4];
+#pragma unroll
+  for (int p = 0; p < (GLU ? 2 : 1); ++p)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[p][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int idx = tid + r * 256;                     // 32 rows x 16 k
+      const int row = idx >> 4, kk = idx & 15;
+      const int ar = arow[row], gk = k0 + kk;
+      As[kk][row] = (ar >= 0 && gk < K) ? to_f32(A[(size_t)ar * lda + gk]) : 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int idx = tid + r * 256;                     // 64 columns x 16 k
+      const int col = idx >> 4, kk = idx & 15;
+      const int gn = n0 + col, gk = k0 + kk;
+      const bool ok = gn < cols && gk < K;
+      Ws[0][kk][col] = ok ? to_f32(We[(size_t)gn * K + gk]) : 0.f;
+      if (GLU) Ws[GLU ? 1 : 0][kk][col] = ok ? to_f32(We[(size_t)(gn + cols) * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MOE_BK; ++kk) {
+      float a[2], b[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) a[i] = As[kk][ty * 2 + i];
+#pragma unroll
+      for (int p = 0; p < (GLU ? 2 : 1); ++p) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Ws[p][kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[p][i][j] = fmaf(a[i], b[j], acc[p][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = ty * 2 + i;
+    if (row >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= cols) continue;
+      float v = acc[0][i][j];
+      if (GLU) v = moe_act(v, act) * acc[GLU ? 1 : 0][i][j];
+      out[(size_t)(r0 + row) * ldo + gn] = from_f32<TO>(v);
+    }
+  }
+}
+
+// A [*][K] (row stride lda).  gather (may be null): row r of the sorted order reads A row gather[r] / gather_div;
+// null: row r itself.  W [E][N][K] contiguous.  out [n][N] (or [n][N / 2] with glu != 0), rows in sorted order.
+// out_dtype: PHOTON_F32 or the input type.  max_tiles: bound of the tile list (the grid's height).
+PHOTON_API int photon_moe_gemm(const void* A, long lda, int dtype, const int* gather, int gather_div, const void* W,
+                               void* out, long ldo, int out_dtype, int N, int K, const int* tiles, const int* num_tiles,
+                               int max_tiles, int glu, int act, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K <= 0 || gather_div <= 0 || (glu && (N & 1))) return PHOTON_ERR_ARGUMENT;
+  if (max_tiles > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const int cols = glu ? N / 2 : N;
+  dim3 grid((cols + MOE_BN - 1) / MOE_BN, max_tiles);
+#define MOE_GEMM(T, TO, GLU) moe_gemm_kernel<T, TO, GLU><<<grid, 256, 0, stream>>>((const T*)A, lda, gather, gather_div, \
+      (const T*)W, (TO*)out, ldo, N, K, tiles, num_tiles, act)
+  if (dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16) { if (glu) MOE_GEMM(bf16, bf16, true); else MOE_GEMM(bf16, bf16, false); }
+  else if (dtype == PHOTON_BF16 && out_dtype == PHOTON_F32) { if (glu) MOE_GEMM(bf16, float, true); else MOE_GEMM(bf16, float, false); }
+  else if (dtype == PHOTON_F32 && out_dtype == PHOTON_F32) { if (glu) MOE_GEMM(float, float, true); else MOE_GEMM(float, float, false); }
+  else return PHOTON_ERR_ARGUMENT;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- weighted sum of the chosen experts
+template <typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const int* __restrict__ place,
+                                   const float* __restrict__ weights, int top, const TO* __restrict__ shared_out,
+                                   TO* __restrict__ out, int H) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j)
+      acc = fmaf(weights[(size_t)t * top + j], y[(size_t)place[(size_t)t * top + j] * ldy + i], acc);
+    if (shared_out) acc += to_f32(shared_out[(size_t)t * H + i]);
+    out[(size_t)t * H + i] = from_f32<TO>(acc);
+  }
+}
+
+// y [n][H] float in sorted order; place, weights [T][top]; shared_out [T][H] (may be null) and out [T][H] of out_dtype.
+PHOTON_API int photon_moe_combine(const float* y, long ldy, const int* place, const float* weights, int top,
+                                  const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (out_dtype == PHOTON_BF16)
+    moe_combine_kernel<bf16><<<T_, threads, 0, stream>>>(y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+  else
+    moe_combine_kernel<float><<<T_, threads, 0, stream>>>(y, ldy, place, weights, top, (const float*)shared_out, (float*)out, H);
+  return launch_status();
+}

@@ -49,7 +49,8 @@ def random_model(config: dict, dtype: str = "bfloat16", device: str = "cuda:0", 
     from ..config.registry import get_architecture
     from ..weights.random_init import random_tensors_on_device
     dev = require_cuda(device)
-    arch = get_architecture((config.get("architectures") or [None])[0])
+    from ..config.registry import architecture_name
+    arch = get_architecture(architecture_name(config))
     cfg = arch.config_class.from_dict(config)
     model = CausalLM(arch.build_spec(cfg), _TORCH_DTYPES[dtype], dev)
     model.config = cfg
@@ -81,7 +82,7 @@ def pages_for(model: CausalLM, options: EngineOptions, max_model_len: int) -> Li
     if options.max_cache_tokens is not None:
         return capped((options.max_cache_tokens + ps - 1) // ps)
     es = torch.empty((), dtype=model.dtype).element_size()
-    page_bytes = [len(entries) * 2 * s.n_kv_heads * s.head_dim * es * ps for s, entries in specs]
+    page_bytes = [len(entries) * s.planes * s.n_kv_heads * s.head_dim * es * ps for s, entries in specs]
     free, _total = torch.cuda.mem_get_info(model.device)
     budget = int(free * options.gpu_memory_fraction)
     # no more than every live request at full length, and no more than 2^20 tokens unless asked for

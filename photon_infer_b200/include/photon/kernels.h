@@ -49,17 +49,28 @@ extern "C" {
 #define PHOTON_DEV_BAD_SLOT 2
 #define PHOTON_DEV_BAD_PAGE 3
 #define PHOTON_DEV_WAIT_TIMEOUT 4
+/* activations of the gated feed-forward kernels: silu, and the tanh form of gelu */
+#define PHOTON_ACT_SILU 0
+#define PHOTON_ACT_GELU_TANH 1
 
 /* ------------------------------------------------------------------ elementwise.cu */
 /* out[t, :] = table[ids[t], :] as float; ids outside [0, V) give a zero row and PHOTON_DEV_BAD_TOKEN. */
 PHOTON_EXPORT int photon_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H, int V, int* err,
                      cudaStream_t stream);
-/* residual (float [*, H], in place) += delta; out = w * residual / sqrt(mean(residual^2) + eps).  delta may be null.
+/* residual (float [*, H], in place) += delta (+ delta2); out = w * residual / sqrt(mean(residual^2) + eps).  delta and
+ * delta2 (same type; the two outputs of a parallel block) may be null.
  * rows (may be null): only these rows are read, nothing is written back, out has one row per entry. */
-PHOTON_EXPORT int photon_add_rmsnorm(const void* delta, int delta_dtype, float* residual, const void* w, int w_dtype, void* out,
-                       int out_dtype, const int* rows, int n, int H, float eps, cudaStream_t stream);
-/* out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I] of one dtype. */
+PHOTON_EXPORT int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                       int w_dtype, void* out, int out_dtype, const int* rows, int n, int H, float eps, cudaStream_t stream);
+/* out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I] of one dtype; act: PHOTON_ACT_*.
+ * photon_swiglu is photon_glu with silu. */
+PHOTON_EXPORT int photon_glu(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream);
 PHOTON_EXPORT int photon_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream);
+/* out [T, 2H] = [residual + delta + delta2 ; other] rounded once to out_dtype (delta, delta2 may be null). */
+PHOTON_EXPORT int photon_stream_concat(const float* residual, const void* delta, const void* delta2, int delta_dtype,
+                         const float* other, void* out, int out_dtype, int T, int H, cudaStream_t stream);
+/* x [T, H] (float, in place) = x * scale + bias; bias [H] of bias_dtype, may be null. */
+PHOTON_EXPORT int photon_scale_bias_rows(float* x, float scale, const void* bias, int bias_dtype, int T, int H, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ rope_kv.cu */
 /* Rotates q [T, n_q * d] and k [T, n_kv * d] in place (rotate != 0; pairs (2j, 2j+1) when interleaved, else
@@ -73,10 +84,59 @@ PHOTON_EXPORT int photon_rope_kv_write(void* q, long q_stride, void* k, long k_s
 PHOTON_EXPORT int photon_rope_table(const float* inv_freq, int half, int count, void* out, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention.cu (float32 and any even head size) */
+/* Values are dv wide: v_cache [num_pages][n_kv][page_size][dv], out [T][n_q * dv]; v_cache == k_cache (dv <= d): the value
+ * of a key is the head of its own row (attention over a cached latent). */
 PHOTON_EXPORT int photon_paged_attention(const void* q, long q_stride, void* out, long out_stride, int dtype, const void* k_cache,
                            const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
-                           const int* positions, int T_, int n_q, int n_kv, int d, int page_size, int num_pages,
+                           const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
                            int window, float scale, int* err, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ latent.cu: attention over a cached latent */
+/* One pass over a token's fused down-projection row down[t] = [query latent (q_rank) | key/value latent (kv_rank) |
+ * shared key part (rot)]: cq[t] = rmsnorm(query latent) * q_norm_w; the cache row at slot_mapping[t] becomes
+ * [rmsnorm(key/value latent) * kv_norm_w | key part with its first rot_dims numbers rotated (i paired with
+ * i + rot_dims / 2, angle positions[t] * inv_freq[i])].  cache: [num_slots][kv_rank + rot]. */
+PHOTON_EXPORT int photon_latent_prep(const void* down, long down_stride, int dtype, int q_rank, int kv_rank, int rot, int rot_dims,
+                       const void* q_norm_w, int q_norm_dtype, const void* kv_norm_w, int kv_norm_dtype, float eps,
+                       const int* positions, const float* inv_freq, const int* slot_mapping, void* cq, long cq_stride,
+                       void* cache, long num_slots, int T_, int* err, cudaStream_t stream);
+/* out[t, h, out_off .. out_off + rot) = the last rot numbers of head h of q [T][heads][dim + rot], rotated as above. */
+PHOTON_EXPORT int photon_latent_q_rope(const void* q, long q_stride, int dtype, int heads, int dim, int rot, int rot_dims,
+                         const int* positions, const float* inv_freq, void* out, long out_stride, int out_head,
+                         int out_off, int T_, cudaStream_t stream);
+/* out[t, h, :] = W[h] x[t, h, :] for every head: x [M][heads][K], out [M][heads][N] (row and head strides in elements),
+ * W [heads][N][K]. */
+PHOTON_EXPORT int photon_head_linear(const void* x, long x_row, long x_head, const void* W, void* out, long o_row, long o_head,
+                       int dtype, int M, int heads, int N, int K, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
+/* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), o_t = S^T (q_t * qscale); out = o_t /
+ * rms(o_t) * norm_w * silu(g_t).  q, k [T][heads * dim] and v, g [T][heads * vdim] share one row stride; z [T][heads * dim]
+ * float; state [num_slots][heads][dim][vdim] float, read from and written to state_slots[s] (negative: starts at zero,
+ * stores nothing). */
+PHOTON_EXPORT int photon_gla_recurrent(const void* q, const void* k, const void* v, const void* g, long in_stride, int dtype,
+                         const float* z, long z_stride, const void* norm_w, int norm_w_dtype, float eps, float tau,
+                         float qscale, const int* cu_tokens, const int* state_slots, float* state, int num_slots,
+                         void* out, long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ moe.cu: routed experts */
+/* Router: logits = Wr h + bias in 32-bit; ids/weights [T][top]: the top experts and the softmax over their logits;
+ * counts [E]: pairs per expert. */
+PHOTON_EXPORT int photon_moe_route(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype, int T_,
+                     int H, int E, int top, int* ids, float* weights, int* counts, cudaStream_t stream);
+/* Stable sort of the n = T * top pairs by expert: offsets [E + 1], sorted [n], place [n], tiles [3 * max_tiles] of
+ * photon_moe_tile_rows() rows at most (expert, first row, rows), num_tiles [1]. */
+PHOTON_EXPORT int photon_moe_align(const int* ids, const int* counts, int n, int E, int* offsets, int* sorted, int* place,
+                     int* tiles, int* num_tiles, cudaStream_t stream);
+PHOTON_EXPORT int photon_moe_tile_rows(void);
+/* Grouped product over the sorted rows with W [E][N][K]; gather (may be null): sorted row r reads A row
+ * gather[r] / gather_div; glu != 0: W = [gate rows; up rows], out [n][N / 2] = act(gate) * up. */
+PHOTON_EXPORT int photon_moe_gemm(const void* A, long lda, int dtype, const int* gather, int gather_div, const void* W, void* out,
+                    long ldo, int out_dtype, int N, int K, const int* tiles, const int* num_tiles, int max_tiles, int glu,
+                    int act, cudaStream_t stream);
+/* out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t]); y [n][H] float. */
+PHOTON_EXPORT int photon_moe_combine(const float* y, long ldy, const int* place, const float* weights, int top,
+                       const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_flash.cu (-DHEAD_DIM=d, d % 16 == 0, <= 128; bfloat16) */
 PHOTON_EXPORT int photon_flash_attention_head_dim(void);

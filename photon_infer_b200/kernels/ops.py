@@ -107,11 +107,17 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Op
 
 
 def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> None:
     """``residual += delta`` in float32 (in place; skipped when ``rows`` is given), then
     ``out = weight * (residual / sqrt(mean(residual^2) + eps))``.  With ``rows`` (int32 list)
-    only those rows are read and ``out`` has one row per list entry."""
-    _cuda(delta, residual, weight, out, rows)
+    only those rows are read and ``out`` has one row per list entry.  ``delta2`` (the second output of a
+    parallel block, same shape and type as ``delta``): ``residual += delta + delta2``."""
+    _cuda(delta, residual, weight, out, rows, delta2)
+    if delta2 is not None:
+        if delta is None:
+            delta, delta2 = delta2, None
+        elif delta2.shape != delta.shape or delta2.dtype != delta.dtype or not delta2.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_rmsnorm: delta2 must match delta")
     H = residual.shape[-1]
     n = rows.numel() if rows is not None else residual.shape[0]
     if residual.dtype != torch.float32 or not residual.is_contiguous():
@@ -123,21 +129,61 @@ def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: t
     if rows is not None:
         _int32(rows, "rows")
     f = _fn("elementwise", "photon_add_rmsnorm",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
-    _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(residual), _ptr(weight),
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(delta2), _ptr(residual), _ptr(weight),
              _dtype_code(weight), _ptr(out), _dtype_code(out), _ptr(rows), n, H, float(eps), _stream()),
            "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """``out = act(gate_up[:, :I]) * gate_up[:, I:]`` with ``act`` silu or the tanh form of gelu."""
     _cuda(gate_up, out)
+    if activation not in ACTIVATIONS:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"unknown activation {activation!r} (silu or gelu_tanh)")
     T, I2 = gate_up.shape
     if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != gate_up.dtype \
             or not gate_up.is_contiguous() or not out.is_contiguous():
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "swiglu: gate_up [T, 2I] and out [T, I] of one dtype")
-    f = _fn("elementwise", "photon_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(gate_up), _ptr(out), _dtype_code(out), T, I2 // 2, _stream()), "swiglu")
+    f = _fn("elementwise", "photon_glu", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _dtype_code(out), T, I2 // 2, ACTIVATIONS[activation], _stream()), "glu")
+
+
+def stream_concat(residual: torch.Tensor, delta: Optional[torch.Tensor], delta2: Optional[torch.Tensor],
+                  other: torch.Tensor, out: torch.Tensor) -> None:
+    """``out [T, 2H] = [residual + delta + delta2 ; other]``: the running stream (its pending sums applied in
+    32-bit) beside a second stream of the same width, rounded once to ``out``'s type."""
+    _cuda(residual, delta, delta2, other, out)
+    T, H = residual.shape
+    if delta is None and delta2 is not None:
+        delta, delta2 = delta2, None
+    for t in (residual, other):
+        if t.dtype != torch.float32 or t.shape != (T, H) or not t.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_concat: both streams must be contiguous float32 [T, H]")
+    for d in (delta, delta2):
+        if d is not None and (d.shape != (T, H) or not d.is_contiguous() or d.dtype != (delta.dtype)):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_concat: the pending sums must be contiguous [T, H] of one type")
+    if out.shape != (T, 2 * H) or not out.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_concat: out must be contiguous [T, 2H]")
+    f = _fn("elementwise", "photon_stream_concat",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _ptr(delta2), _dtype_code(delta) if delta is not None else _dtype_code(out),
+             _ptr(other), _ptr(out), _dtype_code(out), T, H, _stream()), "stream_concat")
+
+
+def scale_bias_rows(x: torch.Tensor, scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
+    """``x [T, H]`` (float32, in place) ``= x * scale + bias``; ``bias [H]`` float32 or bfloat16, may be None."""
+    _cuda(x, bias)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "scale_bias_rows: x must be contiguous float32 [T, H]")
+    T, H = x.shape
+    if bias is not None and (bias.numel() != H or not bias.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "scale_bias_rows: bias must be contiguous [H]")
+    f = _fn("elementwise", "photon_scale_bias_rows", [c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), float(scale), _ptr(bias), _dtype_code(bias) if bias is not None else F32, T, H, _stream()),
+           "scale_bias_rows")
 
 
 # ----------------------------------------------------------------------------- rope and cache write
@@ -198,28 +244,32 @@ def rope_kv_write(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optio
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float,
-                    err: Optional[torch.Tensor]) -> None:
+                    err: Optional[torch.Tensor], value_dim: Optional[int] = None) -> None:
     """General paged causal attention.  ``q`` is a ``[T, n_q * d]`` view (row stride free),
-    ``out [T, n_q * d]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
-    ``max(0, p - window + 1) .. p`` through ``block_table[seq]``."""
+    ``out [T, n_q * dv]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
+    ``max(0, p - window + 1) .. p`` through ``block_table[seq]``.  ``value_dim`` (default ``head_dim``) is the
+    width of a value; ``v_cache is k_cache`` means that a key's value is the first ``value_dim`` numbers of
+    its own row (attention over a cached latent)."""
     _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
     T = q.shape[0]
-    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or out.stride(1) != 1:
-        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "paged_attention: q and out must be [T, n_q * head_dim]")
+    dv = head_dim if value_dim is None else int(value_dim)
+    shared = v_cache is k_cache or v_cache.data_ptr() == k_cache.data_ptr()
+    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * dv) or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "paged_attention: q must be [T, n_q * head_dim], out [T, n_q * value_dim]")
     if q.dtype != out.dtype or q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
         raise PhotonError(ErrorCode.INVALID_ARGUMENT, "paged_attention: q, out and the caches must share one dtype")
-    if n_kv <= 0 or n_q % n_kv or head_dim % 2:
-        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "paged_attention: n_q must be a multiple of n_kv and head_dim even")
-    if (n_q // n_kv) * head_dim > 4096:
-        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE,
-                          f"paged_attention: heads per group x head_dim = {(n_q // n_kv) * head_dim} exceeds 4096")
+    if n_kv <= 0 or n_q % n_kv or dv <= 0 or (shared and dv > head_dim):
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "paged_attention: n_q must be a multiple of n_kv, and a value that "
+                          "lies in its key's row cannot be wider than the row")
+    if k_cache.shape[3] != head_dim or (not shared and v_cache.shape[3] != dv):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "paged_attention: the caches' last dimension must be head_dim / value_dim")
     for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
         _int32(t, name)
     f = _fn("attention", "photon_paged_attention",
             [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
-             _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim,
+             _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim, dv,
              k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), _ptr(err), _stream()),
            "paged_attention")
 
@@ -571,12 +621,16 @@ def skinny_fused(residual: torch.Tensor, delta: Optional[torch.Tensor], norm_wei
     return out, new_residual
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(x Wg^T) * (x Wu^T)`` with ``w_gate_up = [Wg; Wu]``: one kernel for few rows, else the
-    product followed by the SwiGLU kernel."""
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """``act(x Wg^T) * (x Wu^T)`` with ``w_gate_up = [Wg; Wu]``: one kernel for few rows, else the
+    product followed by the gated-activation kernel.  The fused epilogues compute silu; another
+    activation takes the product followed by the activation kernel at every size."""
     M = x.shape[0]
     I = w_gate_up.shape[0] // 2
     out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    if activation != "silu":
+        swiglu(linear(x, w_gate_up), out, activation)
+        return out
     if M <= SKINNY_MAX_ROWS and skinny_gemm_supported(x, w_gate_up, swiglu=True):
         skinny_gemm(x, w_gate_up, out, "swiglu")
         return out
@@ -749,6 +803,188 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         return torch.mm(x, weight.t())
     torch.mm(x, weight.t(), out=out)
     return out
+
+
+# ----------------------------------------------------------------------------- attention over a cached latent
+
+def latent_prep(down: torch.Tensor, q_rank: int, kv_rank: int, rot: int, rot_dims: int, q_norm_w: torch.Tensor,
+                kv_norm_w: torch.Tensor, eps: float, positions: torch.Tensor, inv_freq: torch.Tensor,
+                slot_mapping: torch.Tensor, cq: torch.Tensor, cache: torch.Tensor, err: Optional[torch.Tensor]) -> None:
+    """One pass over the fused down-projection rows ``down [T, q_rank + kv_rank + rot]``: the normed query latent
+    goes to ``cq [T, q_rank]``, the normed key/value latent and the rotated shared key part to the cache row
+    ``slot_mapping[t]`` of ``cache [pages, 1, page_size, kv_rank + rot]``."""
+    _cuda(down, q_norm_w, kv_norm_w, positions, inv_freq, slot_mapping, cq, cache, err)
+    T = down.shape[0]
+    width = kv_rank + rot
+    if down.shape[1] != q_rank + width or down.stride(1) != 1 or cq.shape != (T, q_rank) or cq.stride(1) != 1 \
+            or cq.dtype != down.dtype or cache.dtype != down.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "latent_prep: down [T, q_rank + kv_rank + rot], cq [T, q_rank], one dtype")
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != width or not cache.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "latent_prep: the cache must be contiguous [pages, 1, page_size, kv_rank + rot]")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2 or rot_dims % 2 or rot_dims > rot:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "latent_prep: inv_freq must be float32 [rot_dims / 2], rot_dims even and <= rot")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    f = _fn("latent", "photon_latent_prep",
+            [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(down), down.stride(0), _dtype_code(down), q_rank, kv_rank, rot, rot_dims, _ptr(q_norm_w),
+             _dtype_code(q_norm_w), _ptr(kv_norm_w), _dtype_code(kv_norm_w), float(eps), _ptr(positions), _ptr(inv_freq),
+             _ptr(slot_mapping), _ptr(cq), cq.stride(0), _ptr(cache), cache.shape[0] * cache.shape[2], T, _ptr(err),
+             _stream()), "latent_prep")
+
+
+def latent_q_rope(q: torch.Tensor, heads: int, dim: int, rot: int, rot_dims: int, positions: torch.Tensor,
+                  inv_freq: torch.Tensor, out: torch.Tensor, out_off: int) -> None:
+    """The last ``rot`` numbers of every head of ``q [T, heads * (dim + rot)]``, rotated, into
+    ``out [T, heads, out_head]`` at offset ``out_off`` of every head."""
+    _cuda(q, positions, inv_freq, out)
+    T = q.shape[0]
+    if q.shape[1] != heads * (dim + rot) or q.stride(1) != 1 or out.dim() != 3 or out.shape[:2] != (T, heads) \
+            or out.stride(2) != 1 or out.stride(1) != out.shape[2] or out.dtype != q.dtype or out_off + rot > out.shape[2]:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "latent_q_rope: q [T, heads * (dim + rot)], out [T, heads, >= out_off + rot]")
+    _int32(positions, "positions")
+    f = _fn("latent", "photon_latent_q_rope",
+            [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int,
+             c_int, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _dtype_code(q), heads, dim, rot, rot_dims, _ptr(positions), _ptr(inv_freq), _ptr(out),
+             out.stride(0), out.shape[2], out_off, T, _stream()), "latent_q_rope")
+
+
+#: From this many rows on the bfloat16 per-head products go to the library's batched product.
+HEAD_LINEAR_LIBRARY_ROWS = 16
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, h, :] = weight[h] @ x[t, h, :]`` for all heads at once: ``x [T, heads, K]`` and
+    ``out [T, heads, N]`` are views with free row and head strides, ``weight [heads, N, K]`` is contiguous.
+    float32 and few rows: this package's kernel (one chain of fused multiply-adds per output); many bfloat16
+    rows: the library's batched product."""
+    _cuda(x, weight, out)
+    T, heads, K = x.shape
+    N = weight.shape[1]
+    if weight.shape != (heads, N, K) or not weight.is_contiguous() or out.shape != (T, heads, N) \
+            or x.stride(2) != 1 or out.stride(2) != 1 or x.dtype != weight.dtype or out.dtype != x.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "head_linear: x [T, heads, K], weight [heads, N, K], out [T, heads, N]")
+    if x.dtype == torch.bfloat16 and T >= HEAD_LINEAR_LIBRARY_ROWS:
+        torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    f = _fn("latent", "photon_head_linear",
+            [c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), x.stride(1), _ptr(weight), _ptr(out), out.stride(0), out.stride(1), _dtype_code(x),
+             T, heads, N, K, _stream()), "head_linear")
+
+
+# ----------------------------------------------------------------------------- gated linear attention
+
+def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, z: torch.Tensor,
+                  norm_w: torch.Tensor, eps: float, tau: float, qscale: float, cu_tokens: torch.Tensor,
+                  state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int,
+                  dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+    """The recurrence of gated linear attention over the tokens of a step, request by request, with the
+    per-head norm and the output gate.  ``q, k [T, heads * dim]`` and ``v, g [T, heads * vdim]`` are sections of
+    one fused row (same row stride), ``z [T, heads * dim]`` float32 decay logits, ``state [slots, heads, dim,
+    vdim]`` float32, ``out [T, heads * vdim]``."""
+    _cuda(q, k, v, g, z, norm_w, cu_tokens, state_slots, state, out, err)
+    T = q.shape[0]
+    for name, t, w in (("q", q, heads * dim), ("k", k, heads * dim), ("v", v, heads * vdim), ("g", g, heads * vdim)):
+        if t.shape != (T, w) or t.stride(1) != 1 or t.stride(0) != q.stride(0) or t.dtype != q.dtype:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gla_recurrent: {name} must be [T, {w}] with the row stride of q")
+    if z.dtype != torch.float32 or z.shape != (T, heads * dim) or z.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: z must be float32 [T, heads * dim]")
+    if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (heads, dim, vdim) or not state.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: state must be contiguous float32 [slots, heads, dim, vdim]")
+    if out.shape != (T, heads * vdim) or out.stride(1) != 1 or out.dtype != q.dtype or norm_w.numel() != vdim:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: out [T, heads * vdim] of q's dtype, norm weight [vdim]")
+    _int32(cu_tokens, "cu_tokens")
+    _int32(state_slots, "state_slots")
+    f = _fn("gla", "photon_gla_recurrent",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_int, c_float, c_float,
+             c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(k), _ptr(v), _ptr(g), q.stride(0), _dtype_code(q), _ptr(z), z.stride(0), _ptr(norm_w),
+             _dtype_code(norm_w), float(eps), float(tau), float(qscale), _ptr(cu_tokens), _ptr(state_slots), _ptr(state),
+             state.shape[0], _ptr(out), out.stride(0), int(num_seqs), heads, dim, vdim, _ptr(err), _stream()),
+           "gla_recurrent")
+
+
+# ----------------------------------------------------------------------------- routed experts
+
+def moe_tile_rows() -> int:
+    return int(load_module("moe").photon_moe_tile_rows())
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """Router logits in 32-bit, the ``top`` experts of every token and the softmax over their logits.  Returns
+    ``(ids int32 [T, top], weights float32 [T, top], counts int32 [E])``."""
+    _cuda(h, w_router, bias)
+    T, H = h.shape
+    E = w_router.shape[0]
+    if w_router.shape != (E, H) or not w_router.is_contiguous() or h.stride(1) != 1 or h.dtype != w_router.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_route: h [T, H] and the router [E, H] of one dtype")
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    counts = torch.empty(E, dtype=torch.int32, device=h.device)
+    f = _fn("moe", "photon_moe_route",
+            [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_void_p])
+    _check(f(_ptr(h), h.stride(0), _dtype_code(h), _ptr(w_router), _ptr(bias),
+             _dtype_code(bias) if bias is not None else F32, T, H, E, int(top), _ptr(ids), _ptr(weights), _ptr(counts),
+             _stream()), "moe_route")
+    return ids, weights, counts
+
+
+def moe_align(ids: torch.Tensor, counts: torch.Tensor):
+    """Sorts the (token, choice) pairs by expert on the device.  Returns ``(offsets [E + 1], sorted [n], place
+    [n], tiles [max_tiles, 3], num_tiles [1], max_tiles)``."""
+    _cuda(ids, counts)
+    n, E = ids.numel(), counts.numel()
+    max_tiles = n // moe_tile_rows() + E
+    dev = ids.device
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    srt = torch.empty(n, dtype=torch.int32, device=dev)
+    place = torch.empty(n, dtype=torch.int32, device=dev)
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    f = _fn("moe", "photon_moe_align",
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(ids), _ptr(counts), n, E, _ptr(offsets), _ptr(srt), _ptr(place), _ptr(tiles), _ptr(num_tiles),
+             _stream()), "moe_align")
+    return offsets, srt, place, tiles, num_tiles, max_tiles
+
+
+def moe_gemm(a: torch.Tensor, gather: Optional[torch.Tensor], gather_div: int, weight: torch.Tensor, out: torch.Tensor,
+             tiles: torch.Tensor, num_tiles: torch.Tensor, max_tiles: int, glu: bool = False,
+             activation: str = "silu") -> None:
+    """Grouped product over rows sorted by expert: ``weight [E, N, K]``; sorted row ``r`` reads row
+    ``gather[r] // gather_div`` of ``a`` (``gather`` None: row ``r``).  ``glu``: ``weight`` holds gate rows
+    then up rows and ``out [n, N / 2] = act(gate) * up``."""
+    _cuda(a, gather, weight, out, tiles, num_tiles)
+    E, N, K = weight.shape
+    if a.shape[1] != K or a.stride(1) != 1 or not weight.is_contiguous() or a.dtype != weight.dtype \
+            or out.stride(1) != 1 or out.shape[1] != (N // 2 if glu else N) or out.dtype not in (a.dtype, torch.float32):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_gemm: a [*, K], weight [E, N, K], out [n, N or N / 2]")
+    f = _fn("moe", "photon_moe_gemm",
+            [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), a.stride(0), _dtype_code(a), _ptr(gather), int(gather_div), _ptr(weight), _ptr(out), out.stride(0),
+             _dtype_code(out), N, K, _ptr(tiles), _ptr(num_tiles), int(max_tiles), int(glu), ACTIVATIONS[activation],
+             _stream()), "moe_gemm")
+
+
+def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared_out: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    """``out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t])``, summed in 32-bit in the order of ``j``."""
+    _cuda(y, place, weights, shared_out, out)
+    T, top = weights.shape
+    H = y.shape[1]
+    if y.dtype != torch.float32 or y.stride(1) != 1 or out.shape != (T, H) or not out.is_contiguous() \
+            or (shared_out is not None and (shared_out.shape != (T, H) or not shared_out.is_contiguous()
+                                            or shared_out.dtype != out.dtype)):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_combine: y float32 [n, H], out and shared_out contiguous [T, H]")
+    f = _fn("moe", "photon_moe_combine",
+            [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), y.stride(0), _ptr(place), _ptr(weights), top, _ptr(shared_out), _ptr(out), _dtype_code(out), T, H,
+             _stream()), "moe_combine")
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -34,15 +34,19 @@ def _build_layer(ls: LayerSpec, encodings: Dict[str, Part]) -> Block:
         mixer_params["position_encoding"] = encodings[key]
     norm1 = create_part("norm", ls.norm1.kind, ls.norm1.params)
     mixer = create_part("mixer", ls.mixer.kind, mixer_params)
-    norm2 = create_part("norm", ls.norm2.kind, ls.norm2.params)
-    ff = create_part("feed_forward", ls.feed_forward.kind, ls.feed_forward.params)
+    norm2 = create_part("norm", ls.norm2.kind, ls.norm2.params) if ls.norm2 is not None else None
+    ff = create_part("feed_forward", ls.feed_forward.kind, ls.feed_forward.params) if ls.feed_forward is not None else None
     return create_part("block", ls.block.kind, dict(ls.block.params, norm1=norm1, mixer=mixer, norm2=norm2,
                                                     feed_forward=ff))
 
 
 def _layer_part_prefixes(ls: LayerSpec) -> Dict[str, str]:
-    return {"norm1": ls.prefix + ls.norm1.prefix, "mixer": ls.prefix + ls.mixer.prefix,
-            "norm2": ls.prefix + ls.norm2.prefix, "feed_forward": ls.prefix + ls.feed_forward.prefix}
+    out = {"norm1": ls.prefix + ls.norm1.prefix, "mixer": ls.prefix + ls.mixer.prefix}
+    if ls.norm2 is not None:
+        out["norm2"] = ls.prefix + ls.norm2.prefix
+    if ls.feed_forward is not None:
+        out["feed_forward"] = ls.prefix + ls.feed_forward.prefix
+    return out
 
 
 class _Skeleton:
@@ -53,12 +57,16 @@ class _Skeleton:
         self.spec = spec
         self.encodings = _build_position_encodings(spec)
         self.blocks: List[Block] = [_build_layer(ls, self.encodings) for ls in spec.layers]
+        self.stream_parts: Dict[str, Part] = {name: create_part("stream", ps.kind, ps.params)
+                                              for name, ps in spec.stream_parts.items()}
         self.final_norm = create_part("norm", spec.final_norm.kind, spec.final_norm.params)
 
     def named_parts(self) -> List[Tuple[str, Part]]:
         out: List[Tuple[str, Part]] = []
         for name, pe in self.encodings.items():
             out.append((self.spec.position_encodings[name].prefix, pe))
+        for name, sp in self.stream_parts.items():
+            out.append((self.spec.stream_parts[name].prefix, sp))
         for ls, block in zip(self.spec.layers, self.blocks):
             prefixes = _layer_part_prefixes(ls)
             for key, part in block.parts().items():
@@ -93,6 +101,7 @@ class CausalLM:
         self.device = torch.device(device)
         self.encodings = sk.encodings
         self.blocks = sk.blocks
+        self.stream_parts = sk.stream_parts
         self.final_norm = sk.final_norm
         self._skeleton = sk
         self.embedding: Optional[torch.Tensor] = None
@@ -130,6 +139,8 @@ class CausalLM:
         total = self.head.numel() * self.head.element_size() + self.final_norm.weight_bytes()
         for e in self.spec.run:
             total += sum(p.weight_bytes() for p in self.blocks[e.layer].parts().values())
+            if e.before is not None:
+                total += self.stream_parts[e.before[0]].weight_bytes()
         return total
 
     # ------------------------------------------------------------------ cache needs
@@ -149,9 +160,14 @@ class CausalLM:
         residual = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(ctx.token_ids, self.embedding, residual, ctx.error_flag)
         if self.spec.embedding_scale is not None:
-            residual.mul_(self.spec.embedding_scale)
+            ops.scale_bias_rows(residual, self.spec.embedding_scale)
+        # the embedding output is kept when a stream part will read it again (the blocks add into `residual` in place)
+        first = residual.clone() if any(e.before is not None for e in self.spec.run) else None
         delta = None
         for entry, cache in zip(self.spec.run, caches):
+            if entry.before is not None:
+                name, index = entry.before
+                residual, delta = self.stream_parts[name].forward(residual, delta, first, index, ctx), None
             residual, delta = self.blocks[entry.layer].forward(residual, delta, ctx, cache)
         n = logit_rows.numel()
         if n == 0:

@@ -19,11 +19,11 @@ class PartSpec:
 
 @dataclasses.dataclass
 class LayerSpec:
-    block: PartSpec                         # arrangement, e.g. kind "pre_norm"
+    block: PartSpec                         # arrangement, e.g. kind "pre_norm" or "parallel"
     norm1: PartSpec
     mixer: PartSpec
-    norm2: PartSpec
-    feed_forward: PartSpec
+    norm2: Optional[PartSpec]               # None: the arrangement has one norm
+    feed_forward: Optional[PartSpec]        # None: a layer without a feed-forward
     prefix: str                             # e.g. "model.layers.3."
 
 
@@ -32,9 +32,12 @@ class RunEntry:
     """One step of the run list.  ``layer`` indexes ``ModelSpec.layers`` and may occur in
     several entries (shared weights, a cache of its own for each entry).  ``kv_from``
     names an EARLIER entry of the run list whose cache this entry reads instead of
-    writing one."""
+    writing one.  ``before``: ``(name, index)`` of a stream part (``ModelSpec.stream_parts``)
+    that works on the residual stream right before this entry, e.g. the entrance of a block
+    of layers that is run several times, with the number of the pass."""
     layer: int
     kv_from: Optional[int] = None
+    before: Optional[tuple] = None
 
 
 @dataclasses.dataclass
@@ -56,12 +59,16 @@ class ModelSpec:
     # logits by ``logit_scale`` after the head (architectures that scale either; None: untouched)
     embedding_scale: Optional[float] = None
     logit_scale: Optional[float] = None
+    # parts that work on the residual stream between layers, by name (see RunEntry.before)
+    stream_parts: Dict[str, PartSpec] = dataclasses.field(default_factory=dict)
 
     def validate(self) -> None:
         from ..errors import ErrorCode, PhotonError
         for i, e in enumerate(self.run):
             if not 0 <= e.layer < len(self.layers):
                 raise PhotonError(ErrorCode.INVALID_CONFIG, f"run entry {i} names layer {e.layer}, which does not exist")
+            if e.before is not None and e.before[0] not in self.stream_parts:
+                raise PhotonError(ErrorCode.INVALID_CONFIG, f"run entry {i} names the stream part {e.before[0]!r}, which the model does not define")
             if e.kv_from is not None:
                 if not 0 <= e.kv_from < i:
                     raise PhotonError(ErrorCode.INVALID_CONFIG,

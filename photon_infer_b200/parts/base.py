@@ -30,11 +30,21 @@ class TensorSpec:
     storage when the file has it; ``"int"`` tensors are integer tables, held as int32.
     ``init`` tells the random-weights mode how to fill it: ``"normal"`` (N(0, std)),
     ``"norm"`` (ones, or 1 + N(0, norm_std)), ``"zeros"``.
+    A dimension of ``-1`` in ``shape`` is a size that the configuration does not give: the weight file decides it
+    (the loader accepts any size there), and the random-weights mode uses ``free_size``.
     """
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
+    free_size: int = 16
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(a == -1 or a == b for a, b in zip(self.shape, shape))
+
+    def concrete_shape(self) -> Tuple[int, ...]:
+        return tuple(self.free_size if a == -1 else a for a in self.shape)
 
 
 # ----------------------------------------------------------------------------- caches
@@ -44,10 +54,17 @@ class PagedCacheSpec:
     """What a mixer needs of the paged cache, per token: keys and values of
     ``n_kv_heads * head_dim`` each.  ``window`` None: every earlier key stays
     visible; an integer: only the last ``window`` keys do, and pages behind the
-    window are given back.  Layers with equal specs share one group of pages."""
+    window are given back.  Layers with equal specs share one group of pages.
+    ``values`` False: one row of ``n_kv_heads * head_dim`` per token and no value rows (a
+    mixer that caches a latent from which it derives keys and values alike)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
+
+    @property
+    def planes(self) -> int:
+        return 2 if self.values else 1
 
 
 @dataclasses.dataclass(frozen=True)
@@ -127,24 +144,37 @@ class Part:
         return 0
 
 
+def delta_pair(delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """What a block hands on to be added to the residual stream: nothing, one tensor, or the two outputs of a
+    parallel block (mixer and feed-forward), which are summed with each other first and then into the stream."""
+    if delta is None:
+        return None, None
+    if isinstance(delta, (tuple, list)):
+        parts = [d for d in delta if d is not None]
+        if len(parts) > 2:
+            raise ValueError("at most two pending outputs can be added to the residual stream")
+        return (parts + [None, None])[0], (parts + [None, None])[1]
+    return delta, None
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """``x`` is the 32-bit residual stream ``[T, H]``; returns the normed rows."""
         raise NotImplementedError
 
-    def add_forward(self, delta: Optional[torch.Tensor], residual: torch.Tensor,
-                    out_dtype: torch.dtype) -> torch.Tensor:
-        """``residual += delta`` (in 32-bit, in place), then ``forward(residual)``."""
-        if delta is not None:
-            residual.add_(delta.to(residual.dtype))
+    def add_forward(self, delta, residual: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """``residual += delta`` (in 32-bit, in place), then ``forward(residual)``.  ``delta``: a tensor, a pair
+        of tensors (``delta_pair``) or None."""
+        d1, d2 = delta_pair(delta)
+        if d1 is not None:
+            residual.add_(d1.to(residual.dtype) + d2.to(residual.dtype) if d2 is not None else d1.to(residual.dtype))
         return self.forward(residual, out_dtype)
 
-    def add_forward_rows(self, delta: Optional[torch.Tensor], residual: torch.Tensor,
-                         rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    def add_forward_rows(self, delta, residual: torch.Tensor, rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """Same as ``add_forward`` for the listed rows only; returns ``[len(rows), H]``."""
         r = residual.index_select(0, rows.long())
-        d = delta.index_select(0, rows.long()) if delta is not None else None
-        return self.add_forward(d, r, out_dtype)
+        d = tuple(x.index_select(0, rows.long()) for x in delta_pair(delta) if x is not None)
+        return self.add_forward(d or None, r, out_dtype)
 
 
 class PositionEncoding(Part):
@@ -187,6 +217,17 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamPart(Part):
+    """A step between two layers that works on the residual stream itself (a projection that mixes the running
+    stream with the embedding output, for instance).  The model calls it before the run-list entries that name it."""
+
+    def forward(self, residual: torch.Tensor, delta, first: torch.Tensor, index: int, ctx: StepContext) -> torch.Tensor:
+        """``residual`` (32-bit) with the pending output ``delta`` of the block before, ``first``: the embedding
+        output of the step (32-bit), ``index``: which of its uses this is.  Returns the new 32-bit stream; nothing
+        stays pending."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of parts in a layer.  ``forward`` gets the 32-bit residual stream
     and the not-yet-added output of the previous block, and returns the same pair, so
@@ -198,6 +239,7 @@ class Block(Part):
     def mixer(self) -> Mixer:
         raise NotImplementedError
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
-                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        """``delta``: what the block before left to be added (a tensor, a pair, or None); returns the stream and
+        what this block leaves to be added."""
         raise NotImplementedError

@@ -1,6 +1,11 @@
-"""Pre-norm arrangement of a layer: ``x += mixer(norm1(x)); x += ff(norm2(x))``
-(src/arch/transformer_block.cpp:199-296).  Each residual sum is handed to the norm
-that follows it, which does both in one pass over the row, in 32-bit."""
+"""Arrangements of a layer.
+
+Pre-norm: ``x += mixer(norm1(x)); x += ff(norm2(x))`` (src/arch/transformer_block.cpp:199-296).
+Parallel: ``h = norm1(x); x += mixer(h) + ff(h)``, one norm whose output both sublayers read; a layer
+without a feed-forward adds the mixer's output alone.
+
+Each residual sum is handed to the norm that follows it, which does both in one pass over the row, in
+32-bit; a parallel block hands on its two outputs as a pair, and that norm forms their sum first."""
 from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
@@ -21,10 +26,13 @@ class PreNormBlock(Block):
     def mixer(self) -> Mixer:
         return self._mixer
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
-                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        if isinstance(delta, (tuple, list)):
+            # the block before was a parallel one: the fused first kernels take one pending tensor
+            h = self.norm1.add_forward(delta, residual, ctx.dtype)
+            a = self._mixer.forward(h, ctx, cache)
         # a part may take the residual sum and the norm into its first kernel (decode steps)
-        if self._mixer.fuses_norm(self.norm1, residual, ctx, cache):
+        elif self._mixer.fuses_norm(self.norm1, residual, ctx, cache):
             a, residual = self._mixer.forward_with_norm(residual, delta, self.norm1, ctx, cache)
         else:
             h = self.norm1.add_forward(delta, residual, ctx.dtype)
@@ -37,4 +45,28 @@ class PreNormBlock(Block):
         return residual, d
 
 
+class ParallelBlock(Block):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, feed_forward: Optional[FeedForward] = None):
+        if norm2 is not None:
+            raise ValueError("a parallel block has one norm")
+        self.norm1, self._mixer, self.feed_forward = norm1, mixer, feed_forward
+
+    def parts(self) -> Dict[str, Part]:
+        p = {"norm1": self.norm1, "mixer": self._mixer}
+        if self.feed_forward is not None:
+            p["feed_forward"] = self.feed_forward
+        return p
+
+    def mixer(self) -> Mixer:
+        return self._mixer
+
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        h = self.norm1.add_forward(delta, residual, ctx.dtype)
+        a = self._mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return residual, a
+        return residual, (a, self.feed_forward.forward(h, ctx))
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("parallel", ParallelBlock)

@@ -1,0 +1,86 @@
+"""Gated linear attention: a recurrent mixer with a matrix-valued state per head.
+
+``q = W_q h * dim^(-1/2)``, ``k = W_k h`` (heads x dim), ``v = W_v h`` (heads x vdim) and a decay per key channel
+``a = sigmoid(z)^(1/tau)`` with ``z = W_a2 (W_a1 h) + b`` (a low-rank projection, laid out heads x dim).  Per head
+
+    S_t = diag(a_t) S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t,
+
+``o_t`` is RMS-normed over vdim with a weight that the heads share, the heads are concatenated, multiplied by
+``silu(W_g h)`` and projected by ``W_o``.  The state starts at zero, is 32-bit, and lives in the request's state
+slot between steps; decays, their logarithms and the recurrence itself are 32-bit.
+
+One fused product gives ``[q | k | v | g | W_a1 h]``; one kernel runs the recurrence over the tokens of a step
+with the norm and the gate in its epilogue.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import LayerCache, Mixer, StateSpec, StepContext, TensorSpec
+from .linear import project
+from .registry import register_mixer
+
+
+class GatedLinearAttention(Mixer):
+    kernel_modules = ("gla",)
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, tau: float, eps: float,
+                 decay_rank: Optional[int] = None):
+        self.hidden_size, self.heads, self.dim, self.vdim = hidden_size, heads, dim, vdim
+        self.tau, self.eps = float(tau), float(eps)
+        self.decay_rank = decay_rank            # None: the weight file decides
+        self.w_in = self.w_a2 = self.b_a2 = self.norm = self.w_o = None
+
+    def required_kernels(self, dtype):
+        mods = list(self.kernel_modules)
+        if dtype == torch.bfloat16:
+            mods.extend(["gemm_skinny", "gemm_tc", "gemm_tc2"])
+        return mods
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        H, n, d, v = self.hidden_size, self.heads, self.dim, self.vdim
+        rank = -1 if self.decay_rank is None else self.decay_rank
+        return [TensorSpec("q", (n * d, H)), TensorSpec("k", (n * d, H)), TensorSpec("v", (n * v, H)),
+                TensorSpec("g", (n * v, H)), TensorSpec("o", (H, n * v)),
+                TensorSpec("norm", (v,), role="vector", init="norm"),
+                TensorSpec("a1", (rank, H)), TensorSpec("a2", (n * d, rank)),
+                TensorSpec("a2.b", (n * d,), role="vector", init="normal")]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if tensors["a1"].shape[0] != tensors["a2"].shape[1]:
+            raise ValueError("the two halves of the decay projection do not fit each other")
+        self.decay_rank = tensors["a1"].shape[0]
+        self.w_in = torch.cat([tensors[n] for n in ("q", "k", "v", "g", "a1")], dim=0).contiguous()
+        self.w_a2 = tensors["a2"].contiguous()
+        self.b_a2 = tensors["a2.b"].contiguous()
+        self.norm = tensors["norm"].contiguous()
+        self.w_o = tensors["o"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_a2, self.w_o))
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        T = h.shape[0]
+        nd, nv = self.heads * self.dim, self.heads * self.vdim
+        fused = project(h, self.w_in)                                    # [T, 2 nd + 2 nv + rank]
+        q, k = fused[:, :nd], fused[:, nd:2 * nd]
+        v, g = fused[:, 2 * nd:2 * nd + nv], fused[:, 2 * nd + nv:2 * nd + 2 * nv]
+        low = fused[:, 2 * nd + 2 * nv:]
+        if low.data_ptr() % 16 or low.stride(0) % 8:
+            low = low.contiguous()                                       # the products want aligned rows
+        z = ops.linear(low, self.w_a2, out_dtype=torch.float32)
+        ops.scale_bias_rows(z, 1.0, self.b_a2)
+        out = torch.empty((T, nv), dtype=h.dtype, device=h.device)
+        ops.gla_recurrent(q, k, v, g, z, self.norm, self.eps, self.tau, self.dim ** -0.5, ctx.cu_tokens, ctx.state_slots,
+                          cache.state, out, ctx.num_seqs, self.heads, self.dim, self.vdim, ctx.error_flag)
+        return project(out, self.w_o)
+
+
+register_mixer("gla", GatedLinearAttention)
+register_mixer("gla_2", GatedLinearAttention)

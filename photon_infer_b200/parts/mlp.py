@@ -1,6 +1,7 @@
-"""Dense SwiGLU feed-forward: ``down(silu(gate(h)) * up(h))``
+"""Dense gated feed-forward: ``down(act(gate(h)) * up(h))``; with ``act`` silu it is SwiGLU
 (src/arch/transformer_block.cpp:282-291; include/photon/ops/kernels/swiglu_kernel.hpp:
-67-76).  Gate and up are one fused matrix on the device, so ``h`` is read once."""
+67-76), with the tanh form of gelu it is GeGLU.  Gate and up are one fused matrix on the
+device, so ``h`` is read once.  The tensor names are parameters."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -19,20 +20,26 @@ class SwiGLUFeedForward(FeedForward):
     def required_kernels(self, dtype):
         return ["elementwise"] + (["gemm_skinny", "gemm_skinny_fused", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (silu or gelu_tanh)")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
+        self.activation = activation
+        self.names = tuple(names)
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         H, I = self.hidden_size, self.intermediate_size
-        return [TensorSpec("gate_proj.weight", (I, H)), TensorSpec("up_proj.weight", (I, H)),
-                TensorSpec("down_proj.weight", (H, I))]
+        g, u, d = self.names
+        return [TensorSpec(g, (I, H)), TensorSpec(u, (I, H)), TensorSpec(d, (H, I))]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        g, u, d = self.names
+        self.w_gate_up = torch.cat([tensors[g], tensors[u]], dim=0).contiguous()
+        self.w_down = tensors[d].contiguous()
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
@@ -44,7 +51,7 @@ class SwiGLUFeedForward(FeedForward):
 
     def fuses_norm(self, norm, residual, ctx) -> bool:
         from .norm import RMSNorm
-        return (self.fuse_norm and isinstance(norm, RMSNorm) and ctx is not None and ctx.dtype == torch.bfloat16
+        return (self.fuse_norm and self.activation == "silu" and isinstance(norm, RMSNorm) and ctx is not None and ctx.dtype == torch.bfloat16
                 and ops.skinny_fused_supported(residual, self.w_gate_up))
 
     def forward_with_norm(self, residual, delta, norm, ctx):
@@ -54,8 +61,9 @@ class SwiGLUFeedForward(FeedForward):
         return project(act, self.w_down), residual
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        act = ops.linear_swiglu(h, self.w_gate_up)
+        act = ops.linear_swiglu(h, self.w_gate_up, self.activation)
         return project(act, self.w_down)
 
 
 register_feed_forward("swiglu", SwiGLUFeedForward)
+register_feed_forward("gated", SwiGLUFeedForward)

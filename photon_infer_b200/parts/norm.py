@@ -9,7 +9,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import Norm, TensorSpec
+from .base import Norm, TensorSpec, delta_pair
 from .registry import register_norm
 
 
@@ -36,12 +36,14 @@ class RMSNorm(Norm):
 
     def add_forward(self, delta, residual, out_dtype):
         out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
-        ops.add_rmsnorm(delta, residual, self.weight, self.eps, out)
+        d1, d2 = delta_pair(delta)
+        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, delta2=d2)
         return out
 
     def add_forward_rows(self, delta, residual, rows, out_dtype):
         out = torch.empty((rows.numel(), residual.shape[1]), dtype=out_dtype, device=residual.device)
-        ops.add_rmsnorm(delta, residual, self.weight, self.eps, out, rows=rows)
+        d1, d2 = delta_pair(delta)
+        ops.add_rmsnorm(d1, residual, self.weight, self.eps, out, rows=rows, delta2=d2)
         return out
 
 

@@ -16,9 +16,10 @@ MIXERS: Dict[str, Callable] = {}
 FEED_FORWARDS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
+STREAM_PARTS: Dict[str, Callable] = {}
 
 _TABLES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS,
-           "position_encoding": POSITION_ENCODINGS, "block": BLOCKS}
+           "position_encoding": POSITION_ENCODINGS, "block": BLOCKS, "stream": STREAM_PARTS}
 
 
 def _register(table_name: str, kind: str, factory: Callable, replace: bool) -> None:
@@ -33,6 +34,7 @@ def register_mixer(kind, factory, replace=False): _register("mixer", kind, facto
 def register_feed_forward(kind, factory, replace=False): _register("feed_forward", kind, factory, replace)
 def register_position_encoding(kind, factory, replace=False): _register("position_encoding", kind, factory, replace)
 def register_block(kind, factory, replace=False): _register("block", kind, factory, replace)
+def register_stream_part(kind, factory, replace=False): _register("stream", kind, factory, replace)
 
 
 def create_part(table_name: str, kind: str, params: dict):
@@ -46,4 +48,4 @@ def create_part(table_name: str, kind: str, params: dict):
 
 
 def _ensure_builtin() -> None:
-    from . import attention, block, mlp, norm, rope  # noqa: F401  (each registers itself)
+    from . import attention, block, gla, latent_attention, mlp, moe, norm, rope, stream  # noqa: F401  (each registers itself)

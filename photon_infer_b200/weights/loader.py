@@ -46,7 +46,7 @@ def check_names_and_shapes(declared: Dict[str, TensorSpec], found: Dict[str, tup
     wrong = []
     for n, spec in declared.items():
         if n in found:
-            if tuple(found[n]) != tuple(spec.shape):
+            if not spec.fits(found[n]):
                 wrong.append(f"{n}: expected {list(spec.shape)}, file has {list(found[n])}")
             elif spec.role == "int" and dtypes[n] in _FLOATS:
                 wrong.append(f"{n}: expected an integer table, file has {dtypes[n]}")

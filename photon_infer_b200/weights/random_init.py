@@ -33,16 +33,17 @@ def _generator(seed: int, name: str) -> torch.Generator:
 def random_tensor(spec: TensorSpec, name: str, seed: int, init_std: float, norm_std: float,
                   dtype: torch.dtype) -> torch.Tensor:
     g = _generator(seed, name)
+    shape = spec.concrete_shape()
     if spec.role == "int":
-        return torch.zeros(spec.shape, dtype=torch.int32)
+        return torch.zeros(shape, dtype=torch.int32)
     if spec.init == "zeros":
-        t = torch.zeros(spec.shape, dtype=torch.float32)
+        t = torch.zeros(shape, dtype=torch.float32)
     elif spec.init == "norm":
-        t = torch.ones(spec.shape, dtype=torch.float32)
+        t = torch.ones(shape, dtype=torch.float32)
         if norm_std > 0:
-            t += norm_std * torch.randn(spec.shape, generator=g, dtype=torch.float32)
+            t += norm_std * torch.randn(shape, generator=g, dtype=torch.float32)
     elif spec.init == "normal":
-        t = init_std * torch.randn(spec.shape, generator=g, dtype=torch.float32)
+        t = init_std * torch.randn(shape, generator=g, dtype=torch.float32)
     else:
         raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"tensor {name}: unknown init {spec.init!r}")
     return t.to(dtype)
@@ -53,8 +54,8 @@ def write_random_model(folder: str, config, seed: int = 0, init_std: float = 0.0
     """``config`` is a typed configuration (e.g. ``LlamaConfig``) or a dict in config.json form."""
     from ..models.model import declared_tensors
     if isinstance(config, dict):
-        name = architecture or (config.get("architectures") or [None])[0]
-        arch = get_architecture(name)
+        from ..config.registry import architecture_name
+        arch = get_architecture(architecture or architecture_name(config))
         config = arch.config_class.from_dict(config)
     else:
         arch = get_architecture(architecture or config.architecture)
@@ -86,18 +87,19 @@ def random_tensors_on_device(declared: Dict[str, TensorSpec], run_dtype: torch.d
         g = torch.Generator(device=dev)
         digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
         g.manual_seed(int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF)
+        shape = spec.concrete_shape()
         if spec.role == "int":
-            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=dev)
+            out[name] = torch.zeros(shape, dtype=torch.int32, device=dev)
             continue
         dtype = torch.float32 if (run_dtype == torch.float32 or spec.role == "vector") else run_dtype
         if spec.init == "zeros":
-            t = torch.zeros(spec.shape, dtype=dtype, device=dev)
+            t = torch.zeros(shape, dtype=dtype, device=dev)
         elif spec.init == "norm":
-            t = torch.ones(spec.shape, dtype=dtype, device=dev)
+            t = torch.ones(shape, dtype=dtype, device=dev)
             if norm_std > 0:
-                t += norm_std * torch.randn(spec.shape, generator=g, dtype=dtype, device=dev)
+                t += norm_std * torch.randn(shape, generator=g, dtype=dtype, device=dev)
         elif spec.init == "normal":
-            t = torch.empty(spec.shape, dtype=dtype, device=dev).normal_(0.0, init_std, generator=g)
+            t = torch.empty(shape, dtype=dtype, device=dev).normal_(0.0, init_std, generator=g)
         else:
             raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"tensor {name}: unknown init {spec.init!r}")
         out[name] = t
