@@ -129,3 +129,74 @@ class TraceSession:
 
 def round64(n: int) -> int:
     return (n + 63) // 64 * 64
+
+
+# ----------------------------------------------------------------------------- Finelix
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, base=10000.0):
+    return dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank,
+                scale=(dim + rot_dim) ** -0.5, rot=dict(base=base, dims=rot_dim))
+
+
+def _moe(experts, top, ff, shared=None):
+    m = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=ff))
+    if shared:
+        m["shared"] = dict(ff=shared)
+    return m
+
+
+# Tiny Finelix configurations that differ in every size, in the order of the layers and in which optional pieces
+# they have.
+TINY_FINELIX: Dict[str, dict] = {
+    # a looped block in the middle (two passes), every kind of mixer and feed-forward, a layer without feed-forward
+    "fx_a": dict(
+        config=dict(architecture="Finelix", vocab=160, width=64, embedding=dict(scale=4.0), norm=dict(eps=1e-5),
+                    layers=[dict(type="gla", mixer=dict(heads=2, dim=16, vdim=24, tau=4.0), mlp=dict(kind="dense", ff=96)),
+                            dict(type="latent_attention", mixer=_latent(3, 16, 8, 20, 32, 24), mlp=_moe(4, 2, 32, 48)),
+                            dict(type="gla_2", mixer=dict(heads=1, dim=32, vdim=16, tau=8.0), mlp=None),
+                            dict(type="latent_attention", mixer=_latent(2, 8, 16, 12, 24, 40, base=500.0),
+                                 mlp=dict(kind="dense", ff=80))],
+                    loop=dict(start=1, stop=3, times=2)),
+        seed=11, init_std=0.1, norm_std=0.1, block_size=16),
+    # no loop; one attention head; every expert chosen and no shared expert; one expert of five with a shared one;
+    # a strong decay (tau 1); pages of 8
+    "fx_b": dict(
+        config=dict(architecture="Finelix", vocab=200, width=96, embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+                    layers=[dict(type="latent_attention", mixer=_latent(1, 24, 16, 24, 40, 16, base=1e6), mlp=_moe(3, 3, 40)),
+                            dict(type="gla", mixer=dict(heads=4, dim=8, vdim=8, tau=1.0), mlp=_moe(5, 1, 24, 16))],
+                    loop=None),
+        seed=12, init_std=0.08, norm_std=0.15, block_size=8),
+    # the whole model is the looped block (three passes); pages of 32; a wide gla head
+    "fx_c": dict(
+        config=dict(architecture="Finelix", vocab=131, width=48, embedding=dict(scale=7.5), norm=dict(eps=2e-5),
+                    layers=[dict(type="latent_attention", mixer=_latent(4, 4, 4, 6, 16, 8), mlp=None),
+                            dict(type="gla_2", mixer=dict(heads=1, dim=72, vdim=40, tau=16.0, decay_rank=6),
+                                 mlp=dict(kind="dense", ff=56))],
+                    loop=dict(start=0, stop=2, times=3)),
+        seed=13, init_std=0.12, norm_std=0.05, block_size=32),
+    # a block that is "looped" once, at the end of the model
+    "fx_d": dict(
+        config=dict(architecture="Finelix", vocab=90, width=32, embedding=dict(scale=2.0), norm=dict(eps=1e-5),
+                    layers=[dict(type="gla", mixer=dict(heads=2, dim=12, vdim=10, tau=2.0), mlp=_moe(2, 1, 16, 8)),
+                            dict(type="latent_attention", mixer=_latent(2, 12, 4, 8, 20, 12), mlp=dict(kind="dense", ff=40))],
+                    loop=dict(start=1, stop=2, times=1)),
+        seed=14, init_std=0.15, norm_std=0.1, block_size=16),
+}
+
+
+def make_finelix_folder(path: str, name: str, dtype: str = "bfloat16") -> str:
+    from photon_infer_b200.weights import write_random_model
+    t = TINY_FINELIX[name]
+    write_random_model(path, t["config"], seed=t["seed"], init_std=t["init_std"], norm_std=t["norm_std"], dtype=dtype)
+    return path
+
+
+_finelix_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def finelix_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
+    from plain.finelix_plain import PlainFinelix
+    key = (folder, tuple(ids))
+    if key not in _finelix_cache:
+        _finelix_cache[key] = PlainFinelix.from_folder(folder).logits(ids)
+    return _finelix_cache[key]
