@@ -17,6 +17,11 @@ Two more workloads go into ``points`` of the same line (``--workloads headline``
 * ``llama8b_*``: the Llama 3.1 8B shape at long context: eight prompts of 16,384 tokens fed in portions
   of 2,048, then 256 decode steps of all eight.
 
+``--design finelix`` measures another thing and leaves the line above as it is: prefill and decode throughput of
+the Finelix decoder (parallel layers of gated linear attention and of attention over a cached latent, dense and
+routed feed-forwards) at two sizes that resemble a real model's layers, beside a Llama decoder of equal width,
+depth and feed-forward size, with each design's own kernels timed alone against their rooflines.
+
 ``--impl reference`` runs lumia431/photon_infer itself where it could be built (``baseline/``); else it
 prints an ``unavailable`` line.
 """
@@ -366,6 +371,9 @@ def main() -> int:
     ap.add_argument("--layers-3b", type=int, default=0, help="fewer layers for the 3B workload (0: all 28)")
     ap.add_argument("--layers-8b", type=int, default=0, help="fewer layers for the 8B workload (0: all 32)")
     ap.add_argument("--batch-8b", type=int, default=8)
+    ap.add_argument("--design", default=None, choices=["finelix"],
+                    help="compare this design with a Llama decoder of equal size instead of running the headline")
+    ap.add_argument("--design-sizes", default="2048,4096", help="widths to run with --design")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -379,6 +387,10 @@ def main() -> int:
     import torch
 
     hbm_peak, tf_peak, peak_src = peaks()
+    if args.design == "finelix":
+        from photon_infer_b200.kernels.design_bench import run_finelix_comparison
+        print(json.dumps(run_finelix_comparison(args, hbm_peak, tf_peak, peak_src)))
+        return 0
     if args.only in ("3b", "8b"):
         fn = run_3b_continuous if args.only == "3b" else run_8b_long
         print(json.dumps({"only": args.only, "points": fn(args, hbm_peak, tf_peak)}))

@@ -70,9 +70,12 @@ class ModelRunner:
                  use_cuda_graphs: bool = False, max_graph_batch: int = 256, max_graphs: int = 48):
         self.model = model
         # A captured step is run once before its capture and replayed with padding rows that repeat a
-        # request; both would advance a mixer's per-request state twice.  Models with such state run
-        # their decode steps as plain launches.
-        self.use_cuda_graphs = use_cuda_graphs and not cache.states.specs
+        # request; both would advance a mixer's per-request state twice.  So the run before the capture
+        # and the padding rows get the state slot -1, which a mixer must honour (start from a zero state,
+        # store nothing; ``Mixer.state_skips_negative_slots``).  A model with a mixer that does not runs
+        # its decode steps as plain launches.
+        stateful = [model.blocks[e.layer].mixer() for i, e in enumerate(model.spec.run) if i in cache.states.specs]
+        self.use_cuda_graphs = use_cuda_graphs and all(getattr(m, "state_skips_negative_slots", False) for m in stateful)
         self.max_graph_batch = max_graph_batch
         self.max_graphs = max_graphs        # graphs kept; the one replayed longest ago goes first
         self._graphs: "collections.OrderedDict[tuple, _DecodeGraph]" = collections.OrderedDict()
@@ -168,7 +171,7 @@ class ModelRunner:
 
     def _build_context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
                        static_input: Optional[torch.Tensor] = None, bound_context: Optional[int] = None,
-                       sampling: Optional[tuple] = None):
+                       sampling: Optional[tuple] = None, stateless_from: Optional[int] = None):
         """Builds every index array of the step in one pinned buffer and copies it to the device once.
         ``widths``: block-table widths to use (default: what the requests need).  ``static_input``: a
         device buffer of the same layout to copy into (for a captured graph).  ``bound_context``: the
@@ -204,6 +207,8 @@ class ModelRunner:
             cu[:] = range(S + 1)
             ctxl[:] = [p + 1 for p in starts]
             slots[:] = [cache.states.slot_of(r) for r in rids]
+            if stateless_from is not None:
+                slots[stateless_from:] = -1         # padding rows of a graph, or all rows of the run before a capture
             w = 0
             for s, e in enumerate(entries):
                 for k in e.want:
@@ -301,7 +306,7 @@ class ModelRunner:
                 self._graphs.popitem(last=False)
         else:
             self._graphs.move_to_end(key)
-        ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound, sampling)
+        ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound, sampling, stateless_from=real)
         if device_tokens is not None:
             # into a view of the graph's input buffer; padding rows repeat the first request's id
             if pad:
@@ -328,8 +333,8 @@ class ModelRunner:
         self._build_context(entries, widths, None, bound, sampling)
         size = self._last_total
         static_input = torch.zeros(size, dtype=torch.int32, device=self.device)
-        ctx, logit_rows, _ = self._build_context(entries, widths, static_input, bound, sampling)
-        # once outside the capture: modules load, cuBLAS makes its workspace
+        ctx, logit_rows, _ = self._build_context(entries, widths, static_input, bound, sampling, stateless_from=0)
+        # once outside the capture: modules load, cuBLAS makes its workspace (no request's state is touched)
         warm = self.model.forward(ctx, self._layer_caches, logit_rows)
         if sampling is not None:
             self._sample(warm)

@@ -110,14 +110,15 @@ PHOTON_EXPORT int photon_head_linear(const void* x, long x_row, long x_head, con
                        int dtype, int M, int heads, int N, int K, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
-/* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), o_t = S^T (q_t * qscale); out = o_t /
- * rms(o_t) * norm_w * silu(g_t).  q, k [T][heads * dim] and v, g [T][heads * vdim] share one row stride; z [T][heads * dim]
- * float; state [num_slots][heads][dim][vdim] float, read from and written to state_slots[s] (negative: starts at zero,
- * stores nothing). */
-PHOTON_EXPORT int photon_gla_recurrent(const void* q, const void* k, const void* v, const void* g, long in_stride, int dtype,
-                         const float* z, long z_stride, const void* norm_w, int norm_w_dtype, float eps, float tau,
-                         float qscale, const int* cu_tokens, const int* state_slots, float* state, int num_slots,
-                         void* out, long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream);
+/* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), z_t = w_a2 low_t + b_a2, o_t = S^T (q_t *
+ * qscale); out = o_t / rms(o_t) * norm_w * silu(g_t).  q, k [T][heads * dim], v, g [T][heads * vdim] and low [T][rank] share
+ * one row stride; w_a2 [heads * dim][rank]; state [num_slots][heads][dim][vdim] float, read from and written to
+ * state_slots[s] (negative: starts at zero, stores nothing). */
+PHOTON_EXPORT int photon_gla_recurrent(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
+                         int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype, const void* norm_w,
+                         int norm_w_dtype, float eps, float tau, float qscale, const int* cu_tokens, const int* state_slots,
+                         float* state, int num_slots, void* out, long out_stride, int S, int heads, int dim, int vdim,
+                         int* err, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ moe.cu: routed experts */
 /* Router: logits = Wr h + bias in 32-bit; ids/weights [T][top]: the top experts and the softmax over their logits;

@@ -1,0 +1,232 @@
+"""Prefill and decode throughput of the Finelix decoder beside a Llama decoder of equal width, depth and
+feed-forward size (``python bench.py --design finelix``), with the parts of a layer timed alone against their
+rooflines.
+
+Random weights drawn on the device, synthetic token ids, bfloat16.  Per size:
+
+* prefill: one request, one portion of 2,048 tokens, the best of three timed steps after a warm-up;
+* decode: 8 requests with 512 tokens in the cache, single-token steps (replayed CUDA graphs);
+* parts: the mixer and the feed-forward of one layer of each kind, alone.  Prefill rows are timed with CUDA
+  events around the call; decode rows as a CUDA graph of the part alone, a buffer larger than L2 written before
+  every replay.  ``frac`` is the part's share of its roofline: for decode rows the bytes it must move (the
+  weights it reads, the cache rows or state it reads and writes) over the measured copy bandwidth; for prefill rows
+  its arithmetic (the products and the attention or recurrence) over the measured bfloat16 tensor throughput.
+"""
+from __future__ import annotations
+
+import sys
+from typing import Dict
+
+import torch
+
+PREFILL, PROMPT, BATCH = 2048, 512, 8
+
+
+def finelix_config(width: int, layers: int) -> dict:
+    """Alternating gated-linear-attention and latent-attention layers; heads of 128; a latent of 512 + 64; dense
+    feed-forwards of 4 x width and routed ones (16 experts, 2 per token, one shared) of the same active size."""
+    heads = width // 128
+    gla = dict(type="gla", mixer=dict(heads=heads, dim=128, vdim=128, tau=16.0), mlp=dict(kind="dense", ff=4 * width))
+    lat = dict(type="latent_attention",
+               mixer=dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=max(768, width * 3 // 8),
+                          scale=192 ** -0.5, rot=dict(base=10000.0, dims=64)),
+               mlp=dict(kind="moe", router=dict(experts=16, top=2), expert=dict(ff=width), shared=dict(ff=2 * width)))
+    return dict(architecture="Finelix", vocab=32000, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-5),
+                layers=[gla if i % 2 == 0 else lat for i in range(layers)], loop=None)
+
+
+def llama_config(width: int, layers: int) -> dict:
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=4 * width, num_hidden_layers=layers,
+                num_attention_heads=width // 128, num_key_value_heads=max(1, width // 512), head_dim=128, vocab_size=32000,
+                max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+
+
+def _time_events(fn, reps: int = 3) -> float:
+    fn()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best * 1e3
+
+
+_flush = None
+
+
+def _time_graph(fn, reps: int = 8) -> float:
+    """Microseconds of ``fn()`` replayed as a CUDA graph, with L2 written over before every replay."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    times = []
+    for _ in range(reps):
+        _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return min(times) * 1e3
+
+
+def _part_bytes(part, kind: str, rows: int) -> int:
+    if kind == "moe":
+        # a step reads the router, the shared expert and the experts that were chosen (all of them at most)
+        expert = (part.w_gate_up[0].numel() + part.w_down[0].numel()) * part.w_down.element_size()
+        used = min(part.experts, rows * part.top)
+        rest = part.weight_bytes() - part.experts * expert
+        return rest + used * expert
+    return part.weight_bytes()
+
+
+def _mixer_numbers(m, kind: str, tokens: int, contexts) -> tuple:
+    """(bytes of cache or state a step over ``contexts`` moves, floating-point operations of ``tokens`` rows)."""
+    w = m.weight_bytes()
+    if kind == "gla":
+        state = len(contexts) * m.heads * m.dim * m.vdim * 4 * 2
+        flops = tokens * (w // 2) * 2 + 5 * tokens * m.heads * m.dim * m.vdim
+        return state, flops
+    pairs = sum(c * (c + 1) // 2 for c in contexts) if tokens > len(contexts) else sum(contexts)
+    if kind == "latent":
+        rows = sum(contexts) * m.width * 2
+        flops = tokens * (w // 2) * 2 + 2 * m.heads * (m.width + m.kv_rank) * pairs
+        return rows, flops
+    rows = sum(contexts) * 2 * m.n_kv * m.head_dim * 2
+    flops = tokens * (w // 2) * 2 + 4 * m.n_q * m.head_dim * pairs
+    return rows, flops
+
+
+def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
+    """The mixer and the feed-forward of the first layer of every kind, alone, in a prefill step and a decode step."""
+    from ..parts.attention import PagedAttention
+    from ..parts.gla import GatedLinearAttention
+    from ..parts.latent_attention import LatentAttention
+    from ..parts.moe import MoEFeedForward
+    model, cache = runner.model, runner.cache
+    H = model.spec.hidden_size
+    out: Dict[str, dict] = {}
+    seen = set()
+    for phase in ("prefill", "decode"):
+        rids = ["x"] if phase == "prefill" else [("y", i) for i in range(BATCH)]
+        from ..engine.runner import StepEntry
+        for r in rids:
+            cache.add_request(r)
+        if phase == "decode":
+            for r in rids:
+                cache.extend(r, PROMPT); cache.commit(r, PROMPT)
+        n = PREFILL if phase == "prefill" else 1
+        entries = [StepEntry(r, [1] * n, []) for r in rids]
+        for e in entries:
+            cache.extend(e.request_id, n)
+        ctx, _, _ = runner._build_context(entries)
+        T = ctx.num_tokens
+        contexts = [PREFILL] if phase == "prefill" else [PROMPT + 1] * BATCH
+        h = torch.randn(T, H, device=model.device).to(model.dtype)
+        timer = _time_events if phase == "prefill" else _time_graph
+        for i, e in enumerate(model.spec.run):
+            block = model.blocks[e.layer]
+            m = block.mixer()
+            kind = {GatedLinearAttention: "gla", LatentAttention: "latent", PagedAttention: "attention"}.get(type(m))
+            ff = block.parts().get("feed_forward")
+            fkind = None if ff is None else ("moe" if isinstance(ff, MoEFeedForward) else "dense")
+            lc = runner._layer_caches[i]
+            if kind and (kind, phase) not in seen:
+                seen.add((kind, phase))
+                us = timer(lambda: m.forward(h, ctx, lc))
+                moved, flops = _mixer_numbers(m, kind, T, contexts)
+                frac = (m.weight_bytes() + moved) / (us * 1e-6) / (hbm_peak * 1e9) if phase == "decode" \
+                    else flops / (us * 1e-6) / (tf_peak * 1e12)
+                out[f"{kind}.{phase}"] = {"us": round(us, 1), "frac": round(frac, 4)}
+            if fkind and (fkind, phase) not in seen:
+                seen.add((fkind, phase))
+                us = timer(lambda: ff.forward(h, ctx))
+                wb = _part_bytes(ff, fkind, T)
+                if fkind == "moe":
+                    expert = (ff.w_gate_up[0].numel() + ff.w_down[0].numel())
+                    active = (ff.weight_bytes() // ff.w_down.element_size() - ff.experts * expert) + ff.top * expert
+                else:
+                    active = ff.weight_bytes() // ff.w_down.element_size()
+                frac = wb / (us * 1e-6) / (hbm_peak * 1e9) if phase == "decode" else 2 * T * active / (us * 1e-6) / (tf_peak * 1e12)
+                out[f"{fkind}_ff.{phase}"] = {"us": round(us, 1), "frac": round(frac, 4)}
+        runner.check_device_errors()
+        for r in rids:
+            cache.free_request(r)
+    return out
+
+
+def _throughput(runner, vocab: int, steps: int, warmup: int) -> dict:
+    from ..engine.runner import StepEntry
+    cache = runner.cache
+    gen = torch.Generator().manual_seed(3)
+    ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+    prompt = ids(PREFILL)
+
+    def prefill_once():
+        cache.add_request("p")
+        runner.step([StepEntry("p", prompt, [PREFILL - 1])])
+        cache.free_request("p")
+    pf_us = _time_events(prefill_once)
+    for i in range(BATCH):
+        cache.add_request(("d", i))
+    runner.step([StepEntry(("d", i), ids(PROMPT), []) for i in range(BATCH)])
+    greedy = ([0.0] * BATCH, [0.0] * BATCH)
+    toks = [ids(BATCH) for _ in range(steps + warmup)]
+    one = lambda k: runner.step([StepEntry(("d", i), [toks[k][i]], [0]) for i in range(BATCH)], sampling=greedy)
+    for k in range(warmup):
+        one(k)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(warmup, warmup + steps):
+        one(k)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    runner.check_device_errors()
+    for i in range(BATCH):
+        cache.free_request(("d", i))
+    return {"prefill_tokens_per_s": round(PREFILL / (pf_us * 1e-6), 1), "prefill_ms": round(pf_us / 1e3, 3),
+            "decode_tokens_per_s": round(BATCH / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 4),
+            "decode_graphs": bool(runner.use_cuda_graphs)}
+
+
+def run_finelix_comparison(args, hbm_peak: float, tf_peak: float, peak_src: str) -> dict:
+    from ..cache.manager import CacheManager  # noqa: F401  (import order: the engine pulls in the CUDA side)
+    from ..config.engine_options import EngineOptions
+    from ..engine.loading import build_cache, random_model
+    from ..engine.runner import ModelRunner
+    steps, warmup = max(8, min(args.steps, 64)), max(args.warmup, 3)
+    layers = {2048: 8, 4096: 4}
+    line = {"design": "finelix", "dtype": args.dtype, "data": "synthetic", "peaks": peak_src,
+            "workload": {"prefill_tokens": PREFILL, "decode_batch": BATCH, "decode_context": PROMPT, "steps": steps,
+                         "warmup": warmup}, "sizes": {}}
+    for width in [int(w) for w in args.design_sizes.split(",") if w]:
+        n_layers = layers.get(width, 4)
+        point = {"layers": n_layers}
+        for name, cfg in (("finelix", finelix_config(width, n_layers)), ("llama", llama_config(width, n_layers))):
+            print(f"[bench] {name} width {width}, {n_layers} layers", file=sys.stderr, flush=True)
+            model = random_model(cfg, args.dtype, seed=0)
+            options = EngineOptions(dtype=args.dtype, block_size=args.block_size,
+                                    max_cache_tokens=BATCH * (PROMPT + 128) + PREFILL + 64, max_sequences=BATCH + 1,
+                                    max_batch_size=BATCH + 1, max_num_batched_tokens=max(PREFILL, BATCH * PROMPT),
+                                    max_model_len=4096, use_cuda_graphs=not args.no_graphs)
+            runner = ModelRunner(model, build_cache(model, options, 4096), 4096, use_cuda_graphs=options.use_cuda_graphs)
+            point[name] = _throughput(runner, cfg.get("vocab", cfg.get("vocab_size")), steps, warmup)
+            point[name]["parts"] = _parts(runner, hbm_peak, tf_peak)
+            del runner, model
+            torch.cuda.empty_cache()
+        line["sizes"][str(width)] = point
+    return line

@@ -877,21 +877,23 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> Non
 
 # ----------------------------------------------------------------------------- gated linear attention
 
-def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, z: torch.Tensor,
-                  norm_w: torch.Tensor, eps: float, tau: float, qscale: float, cu_tokens: torch.Tensor,
-                  state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int,
-                  dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
-    """The recurrence of gated linear attention over the tokens of a step, request by request, with the
-    per-head norm and the output gate.  ``q, k [T, heads * dim]`` and ``v, g [T, heads * vdim]`` are sections of
-    one fused row (same row stride), ``z [T, heads * dim]`` float32 decay logits, ``state [slots, heads, dim,
-    vdim]`` float32, ``out [T, heads * vdim]``."""
-    _cuda(q, k, v, g, z, norm_w, cu_tokens, state_slots, state, out, err)
+def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor,
+                  w_a2: torch.Tensor, b_a2: torch.Tensor, norm_w: torch.Tensor, eps: float, tau: float, qscale: float,
+                  cu_tokens: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                  num_seqs: int, heads: int, dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+    """The recurrence of gated linear attention over the tokens of a step, request by request, with the decay
+    logits ``w_a2 low + b_a2``, the per-head norm and the output gate.  ``q, k [T, heads * dim]``,
+    ``v, g [T, heads * vdim]`` and ``low [T, rank]`` are sections of one fused row (same row stride),
+    ``w_a2 [heads * dim, rank]``, ``state [slots, heads, dim, vdim]`` float32, ``out [T, heads * vdim]``."""
+    _cuda(q, k, v, g, low, w_a2, b_a2, norm_w, cu_tokens, state_slots, state, out, err)
     T = q.shape[0]
-    for name, t, w in (("q", q, heads * dim), ("k", k, heads * dim), ("v", v, heads * vdim), ("g", g, heads * vdim)):
+    rank = low.shape[1]
+    for name, t, w in (("q", q, heads * dim), ("k", k, heads * dim), ("v", v, heads * vdim), ("g", g, heads * vdim),
+                       ("low", low, rank)):
         if t.shape != (T, w) or t.stride(1) != 1 or t.stride(0) != q.stride(0) or t.dtype != q.dtype:
             raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gla_recurrent: {name} must be [T, {w}] with the row stride of q")
-    if z.dtype != torch.float32 or z.shape != (T, heads * dim) or z.stride(1) != 1:
-        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: z must be float32 [T, heads * dim]")
+    if w_a2.shape != (heads * dim, rank) or not w_a2.is_contiguous() or w_a2.dtype != q.dtype or b_a2.numel() != heads * dim:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: w_a2 [heads * dim, rank] of q's dtype, b_a2 [heads * dim]")
     if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (heads, dim, vdim) or not state.is_contiguous():
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gla_recurrent: state must be contiguous float32 [slots, heads, dim, vdim]")
     if out.shape != (T, heads * vdim) or out.stride(1) != 1 or out.dtype != q.dtype or norm_w.numel() != vdim:
@@ -899,12 +901,13 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
     _int32(cu_tokens, "cu_tokens")
     _int32(state_slots, "state_slots")
     f = _fn("gla", "photon_gla_recurrent",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_int, c_float, c_float,
-             c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(q), _ptr(k), _ptr(v), _ptr(g), q.stride(0), _dtype_code(q), _ptr(z), z.stride(0), _ptr(norm_w),
-             _dtype_code(norm_w), float(eps), float(tau), float(qscale), _ptr(cu_tokens), _ptr(state_slots), _ptr(state),
-             state.shape[0], _ptr(out), out.stride(0), int(num_seqs), heads, dim, vdim, _ptr(err), _stream()),
-           "gla_recurrent")
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
+             c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(low), q.stride(0), _dtype_code(q), rank, _ptr(w_a2), _ptr(b_a2),
+             _dtype_code(b_a2), _ptr(norm_w), _dtype_code(norm_w), float(eps), float(tau), float(qscale), _ptr(cu_tokens),
+             _ptr(state_slots), _ptr(state), state.shape[0], _ptr(out), out.stride(0), int(num_seqs), heads, dim, vdim,
+             _ptr(err), _stream()), "gla_recurrent")
 
 
 # ----------------------------------------------------------------------------- routed experts

@@ -184,6 +184,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: True when the mixer treats a negative state slot as "start from a zero state and store nothing"; decode
+    #: steps of a model whose stateful mixers all do are replayed as CUDA graphs.
+    state_skips_negative_slots = False
+
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         return None
 

@@ -9,8 +9,8 @@
 ``silu(W_g h)`` and projected by ``W_o``.  The state starts at zero, is 32-bit, and lives in the request's state
 slot between steps; decays, their logarithms and the recurrence itself are 32-bit.
 
-One fused product gives ``[q | k | v | g | W_a1 h]``; one kernel runs the recurrence over the tokens of a step
-with the norm and the gate in its epilogue.
+One fused product gives ``[q | k | v | g | W_a1 h]``; one kernel forms the decay logits from the low-rank part,
+runs the recurrence over the tokens of a step and applies the norm and the gate in its epilogue.
 """
 from __future__ import annotations
 
@@ -26,6 +26,7 @@ from .registry import register_mixer
 
 class GatedLinearAttention(Mixer):
     kernel_modules = ("gla",)
+    state_skips_negative_slots = True
 
     def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, tau: float, eps: float,
                  decay_rank: Optional[int] = None):
@@ -72,13 +73,10 @@ class GatedLinearAttention(Mixer):
         q, k = fused[:, :nd], fused[:, nd:2 * nd]
         v, g = fused[:, 2 * nd:2 * nd + nv], fused[:, 2 * nd + nv:2 * nd + 2 * nv]
         low = fused[:, 2 * nd + 2 * nv:]
-        if low.data_ptr() % 16 or low.stride(0) % 8:
-            low = low.contiguous()                                       # the products want aligned rows
-        z = ops.linear(low, self.w_a2, out_dtype=torch.float32)
-        ops.scale_bias_rows(z, 1.0, self.b_a2)
         out = torch.empty((T, nv), dtype=h.dtype, device=h.device)
-        ops.gla_recurrent(q, k, v, g, z, self.norm, self.eps, self.tau, self.dim ** -0.5, ctx.cu_tokens, ctx.state_slots,
-                          cache.state, out, ctx.num_seqs, self.heads, self.dim, self.vdim, ctx.error_flag)
+        ops.gla_recurrent(q, k, v, g, low, self.w_a2, self.b_a2, self.norm, self.eps, self.tau, self.dim ** -0.5,
+                          ctx.cu_tokens, ctx.state_slots, cache.state, out, ctx.num_seqs, self.heads, self.dim, self.vdim,
+                          ctx.error_flag)
         return project(out, self.w_o)
 
 

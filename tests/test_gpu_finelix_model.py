@@ -161,18 +161,22 @@ def test_long_decoding(session):
         session.collected.pop("long", None)
 
 
-@pytest.mark.parametrize("name", ["fx_a", "fx_b", "fx_d"])
-def test_greedy_generation_through_the_engine(tmp_path, name):
-    """Requests of unequal length through ``ContinuousBatchEngine`` (scheduler, portions of 16 tokens, two state slots
-    for three requests): the tokens are those of the plain implementation's greedy loop."""
+@pytest.mark.parametrize("name,lengths,slots", [("fx_a", (37, 5, 18), 2), ("fx_b", (37, 5, 18), 2), ("fx_d", (37, 5, 18), 2),
+                                                ("fx_a", (9, 30, 4, 21, 13), 5), ("fx_c", (3, 12, 7), 3)])
+def test_greedy_generation_through_the_engine(tmp_path, name, lengths, slots):
+    """Requests of unequal length through ``ContinuousBatchEngine`` (scheduler, portions of 16 tokens, fewer state
+    slots than requests, or as many): the tokens are those of the plain implementation's greedy loop.  The decode
+    steps replay CUDA graphs; with five or three live requests the batch is padded to the next captured size, and
+    neither the padding rows nor the run before a capture may touch a request's recurrent state."""
     from photon_infer_b200 import ContinuousBatchEngine, EngineOptions
     from plain.finelix_plain import PlainFinelix
     folder = make_finelix_folder(str(tmp_path / name), name)
     vocab = TINY_FINELIX[name]["config"]["vocab"]
-    prompts = [random_ids(n, vocab, seed=n) for n in (37, 5, 18)]
+    prompts = [random_ids(n, vocab, seed=n) for n in lengths]
     engine = ContinuousBatchEngine(folder, EngineOptions(dtype="float32", block_size=TINY_FINELIX[name]["block_size"],
-                                                         max_cache_tokens=256, max_sequences=2, chunk_size=16,
+                                                         max_cache_tokens=64 * slots + 128, max_sequences=slots, chunk_size=16,
                                                          max_num_batched_tokens=24, max_model_len=128))
+    assert engine.runner.use_cuda_graphs
     rids = [engine.add_request(p, max_new_tokens=10, temperature=0.0, ignore_eos=True) for p in prompts]
     out = engine.run_until_complete()
     plain = PlainFinelix.from_folder(folder)

@@ -279,14 +279,27 @@ def test_paged_attention_reports_missing_page():
     assert err.cpu().tolist()[0] == 3
 
 
-def test_paged_attention_refuses_oversized_group():
+def test_paged_attention_takes_any_number_of_heads_per_group():
+    """64 query heads of 128 on one key/value head: the heads are run in chunks that fit a block.  A head wider
+    than a block's shared memory allows is refused."""
     from photon_infer_b200.errors import PhotonError
     from photon_infer_b200.kernels import ops
-    z = torch.zeros(1, 64 * 128, device=DEV)
-    kc = torch.zeros(1, 1, 8, 128, device=DEV)
+    torch.manual_seed(21)
+    n_q, d, ps, n = 64, 128, 8, 21
+    q = torch.randn(1, n_q * d, device=DEV)
+    kc, vc = torch.randn(3, 1, ps, d, device=DEV), torch.randn(3, 1, ps, d, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, n_q * d, device=DEV)
+    ops.paged_attention(q, out, kc, vc, i32([[2, 0, 1]]), i32([0]), i32([n - 1]), n_q, 1, d, None, 0.1, None)
+    keys = torch.cat([kc[2, 0], kc[0, 0], kc[1, 0]])[:n].double()
+    vals = torch.cat([vc[2, 0], vc[0, 0], vc[1, 0]])[:n].double()
+    want = torch.softmax(q.double().view(n_q, d) @ keys.T * 0.1, dim=1) @ vals
+    assert float((out.double().view(n_q, d) - want).abs().max()) < 1e-5
+    z = torch.zeros(1, 4098, device=DEV)
+    kw = torch.zeros(1, 1, 8, 4098, device=DEV)
     i = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(PhotonError):
-        ops.paged_attention(z, z.clone(), kc, kc, i.view(1, 1), i, i, 64, 1, 128, None, 1.0, None)
+        ops.paged_attention(z, z.clone(), kw, kw, i.view(1, 1), i, i, 1, 1, 4098, None, 1.0, None)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1, 1), (1, 300, 77), (65, 64, 16), (130, 257, 1000), (7, 389, 120)])
