@@ -34,7 +34,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const int* __restrict__ block_table, int max_pages,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        int n_q, int n_kv, int d, int dv, int hb, int page_size, int num_pages, int window,
-                       float scale, int* err) {
+                       float scale, int splits, float* __restrict__ part, int* err) {
   extern __shared__ __align__(16) float smem[];
   const int chunks = (n_q / n_kv + hb - 1) / hb;
   const int t = blockIdx.x, g = blockIdx.y / chunks;
@@ -67,7 +67,16 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 #pragma unroll
   for (int n = 0; n < PPT; ++n) acc[n] = 0.f;
 
-  for (int tile0 = (kstart / ATT_TILE) * ATT_TILE; tile0 <= p; tile0 += ATT_TILE) {
+  // the key tiles of this block: all of them, or one of `splits` equal shares (blockIdx.z)
+  int tile_lo = kstart / ATT_TILE, tile_hi = p / ATT_TILE + 1;
+  if (splits > 1) {
+    const int per = (tile_hi - tile_lo + splits - 1) / splits;
+    tile_lo += blockIdx.z * per;
+    tile_hi = min(tile_hi, tile_lo + per);
+  }
+  constexpr int VEC = 16 / sizeof(T);
+  const bool vec = (d % VEC == 0) && ((uintptr_t)k_cache % 16 == 0);
+  for (int tile0 = tile_lo * ATT_TILE; tile0 < tile_hi * ATT_TILE; tile0 += ATT_TILE) {
     __syncthreads();                          // previous tile fully consumed; qs ready on the first pass
     if (tid < ATT_TILE) {
       const int kk = tile0 + tid;
@@ -83,10 +92,24 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
       kbase[tid] = base;
     }
     __syncthreads();
-    for (int i = tid; i < ATT_TILE * d; i += ATT_THREADS) {
-      const int key = i / d, j = i - key * d;
-      const long long base = kbase[key];
-      ks[key * (d + 1) + j] = base >= 0 ? to_f32(k_cache[base + j]) : 0.f;
+    if (vec) {
+      const int per_key = d / VEC;
+#pragma unroll 4
+      for (int i = tid; i < ATT_TILE * per_key; i += ATT_THREADS) {
+        const int key = i / per_key, j = (i - key * per_key) * VEC;
+        const long long base = kbase[key];
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (base >= 0) raw = *reinterpret_cast<const uint4*>(k_cache + base + j);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) ks[key * (d + 1) + j + u] = to_f32(e[u]);
+      }
+    } else {
+      for (int i = tid; i < ATT_TILE * d; i += ATT_THREADS) {
+        const int key = i / d, j = i - key * d;
+        const long long base = kbase[key];
+        ks[key * (d + 1) + j] = base >= 0 ? to_f32(k_cache[base + j]) : 0.f;
+      }
     }
     if (!shared_kv) {
       for (int i = tid; i < ATT_TILE * dv; i += ATT_THREADS) {
@@ -145,8 +168,38 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
     if (i < G * dv) {
       const int h = i / dv, j = i - h * dv;
       const float l = lsum[h];
-      out[(size_t)t * out_stride + (size_t)(h0 + h) * dv + j] = from_f32<T>(l > 0.f ? acc[n] / l : 0.f);
+      if (splits > 1) {
+        // this share's sums as they stand, with the head's running maximum and denominator behind them
+        float* dst = part + (((size_t)t * n_q + h0 + h) * splits + blockIdx.z) * (dv + 2);
+        dst[j] = acc[n];
+        if (j == 0) { dst[dv] = mrun[h]; dst[dv + 1] = l; }
+      } else {
+        out[(size_t)t * out_stride + (size_t)(h0 + h) * dv + j] = from_f32<T>(l > 0.f ? acc[n] / l : 0.f);
+      }
     }
+  }
+}
+
+// The shares of one (token, head) put together, in the order of the shares.
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part, int splits, int dv, T* __restrict__ out,
+                                       long out_stride, int n_q) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* src = part + ((size_t)t * n_q + h) * splits * (dv + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[s * (dv + 2) + dv]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = src[s * (dv + 2) + dv];
+    if (ms != -INFINITY) l += src[s * (dv + 2) + dv + 1] * expf(ms - m);
+  }
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = src[s * (dv + 2) + dv];
+      if (ms != -INFINITY) a += src[s * (dv + 2) + j] * expf(ms - m);
+    }
+    out[(size_t)t * out_stride + (size_t)h * dv + j] = from_f32<T>(l > 0.f ? a / l : 0.f);
   }
 }
 
@@ -154,7 +207,8 @@ template <typename T, int PPT>
 static int attention_launch(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                             const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                             const int* positions, int T_, int n_q, int n_kv, int d, int dv, int hb, int page_size,
-                            int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+                            int num_pages, int window, float scale, int splits, float* part, int* err,
+                            cudaStream_t stream) {
   const int G = hb;
   const size_t floats = (size_t)G * d + ATT_TILE * (d + 1) + (v_cache == k_cache ? 0 : ATT_TILE * dv) +
                         (size_t)G * ATT_TILE + 3 * G + 1;
@@ -165,10 +219,13 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(T_, n_kv * ((n_q / n_kv + hb - 1) / hb));
+  dim3 grid(T_, n_kv * ((n_q / n_kv + hb - 1) / hb), splits);
   paged_attention_kernel<T, PPT><<<grid, ATT_THREADS, smem, stream>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_table,
-      max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, err);
+      max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err);
+  int st = launch_status();
+  if (st != 0 || splits <= 1) return st;
+  attention_merge_kernel<T><<<dim3(T_, n_q), 128, 0, stream>>>(part, splits, dv, (T*)out, out_stride, n_q);
   return launch_status();
 }
 
@@ -182,17 +239,22 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
   return PHOTON_ERR_UNSUPPORTED;
 
 #define ATT_ARGS q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, token_seq, \
-                 positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, err, stream
+                 positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err, stream
 
 // window <= 0: all keys.  Strides in elements.  The key cache holds [num_pages][n_kv][page_size][d], the value
 // cache [num_pages][n_kv][page_size][dv]; v_cache == k_cache (dv <= d): a key's value is the head of its row.
 // out [T][n_q * dv].  A block runs up to 4096 / max(d, dv) of the query heads that share a key/value head.
+// splits > 1: the key tiles of every token are shared out over that many blocks (decoded tokens with long
+// contexts, where one block per token and head chunk leaves the GPU empty); part: float scratch of
+// T * n_q * splits * (dv + 2); a second kernel puts the shares together in their order.
 PHOTON_API int photon_paged_attention(const void* q, long q_stride, void* out, long out_stride, int dtype,
                                       const void* k_cache, const void* v_cache, const int* block_table,
                                       int max_pages, const int* token_seq, const int* positions, int T_,
                                       int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window,
-                                      float scale, int* err, cudaStream_t stream) {
+                                      float scale, int splits, float* part, int* err, cudaStream_t stream) {
   if (T_ <= 0) return 0;
+  if (splits < 1 || splits > 64 || (splits > 1 && part == nullptr) || T_ > 65535 * 32) return PHOTON_ERR_ARGUMENT;
+  if (splits > 1 && n_q > 65535) return PHOTON_ERR_UNSUPPORTED;
   if (n_kv <= 0 || n_q % n_kv || d <= 0 || dv <= 0 || page_size <= 0) return PHOTON_ERR_ARGUMENT;
   if (v_cache == k_cache && dv > d) return PHOTON_ERR_ARGUMENT;
   if (d > 4096 || dv > 4096) return PHOTON_ERR_UNSUPPORTED;

@@ -207,3 +207,70 @@ PHOTON_API int photon_head_linear(const void* x, long x_row, long x_head, const 
                                                        o_row, o_head, M, N, K);
   return launch_status();
 }
+
+// ---------------------------------------------------------------- a request's cached rows, in order
+// out[p, :] = cache[table[p / page_size] * page_size + p % page_size, :] for p < count: the latent rows of one
+// request as one dense matrix, the operand of the products that attention over a long prompt portion is made of.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ cache, const int* __restrict__ table, int page_size,
+                                   int num_pages, int width, int count, T* __restrict__ out, int* err) {
+  const int p = blockIdx.x;
+  const int page = table[p / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) report_error(err, PHOTON_DEV_BAD_PAGE, 0, p, page);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)p * width + i] = from_f32<T>(0.f);
+    return;
+  }
+  const T* src = cache + ((size_t)page * page_size + p % page_size) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)p * width + i] = src[i];
+}
+
+PHOTON_API int photon_gather_rows(const void* cache, int dtype, const int* table, int page_size, int num_pages,
+                                  int width, int count, void* out, int* err, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (page_size <= 0 || width <= 0) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_BF16)
+    gather_rows_kernel<bf16><<<count, 128, 0, stream>>>((const bf16*)cache, table, page_size, num_pages, width, count, (bf16*)out, err);
+  else
+    gather_rows_kernel<float><<<count, 128, 0, stream>>>((const float*)cache, table, page_size, num_pages, width, count, (float*)out, err);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- causal softmax over rows of scores
+// scores [rows][ld] float: row r belongs to the token at position first_pos + r / heads, which sees the keys
+// 0 .. its own position.  probs [rows][ldp] = softmax(scale * scores) over the visible keys, zero beyond them, up to
+// column `cols`.  One block per row, 32-bit throughout, rounded once on the way out.
+template <typename T>
+__global__ void causal_softmax_kernel(const float* __restrict__ scores, long ld, T* __restrict__ probs, long ldp,
+                                      int heads, int first_pos, int cols, float scale) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int visible = min(cols, first_pos + r / heads + 1);
+  const float* s = scores + (size_t)r * ld;
+  T* p = probs + (size_t)r * ldp;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < visible; i += blockDim.x) m = fmaxf(m, s[i] * scale);
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : -INFINITY;
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < visible; i += blockDim.x) sum += expf(s[i] * scale - m);
+  sum = block_sum(sum, red);
+  const float inv = 1.0f / sum;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x)
+    p[i] = from_f32<T>(i < visible ? expf(s[i] * scale - m) * inv : 0.f);
+}
+
+PHOTON_API int photon_causal_softmax_rows(const float* scores, long ld, void* probs, long ldp, int dtype, int rows,
+                                          int heads, int first_pos, int cols, float scale, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (heads <= 0 || first_pos < 0) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_BF16)
+    causal_softmax_kernel<bf16><<<rows, 256, 0, stream>>>(scores, ld, (bf16*)probs, ldp, heads, first_pos, cols, scale);
+  else
+    causal_softmax_kernel<float><<<rows, 256, 0, stream>>>(scores, ld, (float*)probs, ldp, heads, first_pos, cols, scale);
+  return launch_status();
+}

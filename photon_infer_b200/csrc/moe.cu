@@ -29,10 +29,22 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
   if (t >= T_) return;
   float* lg = logits + warp * E;
   const T* x = h + (size_t)t * h_stride;
+  constexpr int V = 16 / sizeof(T);                      // elements of a 16-byte load
+  const bool vec = (H % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)Wr % 16 == 0);
   for (int e = 0; e < E; ++e) {
     const T* w = Wr + (size_t)e * H;
     float acc = 0.f;
-    for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(x[k]), to_f32(w[k]), acc);
+    if (vec) {
+      for (int k = lane * V; k < H; k += 32 * V) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + k), wv = *reinterpret_cast<const uint4*>(w + k);
+        const T* xp = reinterpret_cast<const T*>(&xv);
+        const T* wp = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc = fmaf(to_f32(xp[i]), to_f32(wp[i]), acc);
+      }
+    } else {
+      for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(x[k]), to_f32(w[k]), acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) lg[e] = acc + (bias ? load_w(bias, bias_bf16, e) : 0.f);
   }
@@ -242,28 +254,133 @@ PHOTON_API int photon_moe_gemm(const void* A, long lda, int dtype, const int* ga
 }
 
 // ---------------------------------------------------------------- weighted sum of the chosen experts
-template <typename TO>
-__global__ void moe_combine_kernel(const float* __restrict__ y, long ldy, const int* __restrict__ place,
+template <typename TY, typename TO>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, long ldy, const int* __restrict__ place,
                                    const float* __restrict__ weights, int top, const TO* __restrict__ shared_out,
                                    TO* __restrict__ out, int H) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
-      acc = fmaf(weights[(size_t)t * top + j], y[(size_t)place[(size_t)t * top + j] * ldy + i], acc);
+      acc = fmaf(weights[(size_t)t * top + j],
+                 to_f32(y[(size_t)(place ? place[(size_t)t * top + j] : t * top + j) * ldy + i]), acc);
     if (shared_out) acc += to_f32(shared_out[(size_t)t * H + i]);
     out[(size_t)t * H + i] = from_f32<TO>(acc);
   }
 }
 
-// y [n][H] float in sorted order; place, weights [T][top]; shared_out [T][H] (may be null) and out [T][H] of out_dtype.
-PHOTON_API int photon_moe_combine(const float* y, long ldy, const int* place, const float* weights, int top,
+// y [n][H] (float or bfloat16): row place[t, j] is the output of token t's j-th expert (place null: row t * top + j);
+// weights [T][top]; shared_out [T][H] (may be null) and out [T][H] of out_dtype.
+PHOTON_API int photon_moe_combine(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
                                   const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  if (out_dtype == PHOTON_BF16)
-    moe_combine_kernel<bf16><<<T_, threads, 0, stream>>>(y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+  if (out_dtype == PHOTON_BF16 && y_dtype == PHOTON_F32)
+    moe_combine_kernel<float, bf16><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+  else if (out_dtype == PHOTON_BF16 && y_dtype == PHOTON_BF16)
+    moe_combine_kernel<bf16, bf16><<<T_, threads, 0, stream>>>((const bf16*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+  else if (out_dtype == PHOTON_F32 && y_dtype == PHOTON_F32)
+    moe_combine_kernel<float, float><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const float*)shared_out, (float*)out, H);
   else
-    moe_combine_kernel<float><<<T_, threads, 0, stream>>>(y, ldy, place, weights, top, (const float*)shared_out, (float*)out, H);
+    return PHOTON_ERR_ARGUMENT;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- rows in sorted order
+// out[r, :] = x[sorted[r] / div, :]: the input rows of the (token, choice) pairs, expert by expert, as the
+// library's grouped product wants them.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ sorted, int div,
+                                  T* __restrict__ out, int H) {
+  const T* src = x + (size_t)(sorted[blockIdx.x] / div) * ldx;
+  T* dst = out + (size_t)blockIdx.x * H;
+  if (H % (16 / sizeof(T)) == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)dst % 16 == 0) {
+    const int n = H / (16 / sizeof(T));
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+PHOTON_API int photon_moe_gather(const void* x, long ldx, int dtype, const int* sorted, int div, void* out, int n, int H,
+                                 cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (div <= 0) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_BF16) moe_gather_kernel<bf16><<<n, 128, 0, stream>>>((const bf16*)x, ldx, sorted, div, (bf16*)out, H);
+  else moe_gather_kernel<float><<<n, 128, 0, stream>>>((const float*)x, ldx, sorted, div, (float*)out, H);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- few rows: one matrix-vector product per pair
+// A decode step brings a handful of (token, choice) pairs, each to another expert as a rule: nothing is sorted,
+// block (c, p) streams the rows c * 32 .. of pair p's expert matrix once, 16 bytes per lane and load, against the
+// pair's input row in shared memory; a warp owns four output features at a time and adds its lanes' sums up.
+#define GEMV_COLS 32
+
+template <typename TO, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(const bf16* __restrict__ x, long ldx, int x_div, const int* __restrict__ ids, const bf16* __restrict__ W,
+                TO* __restrict__ out, long ldo, int N, int K, int act) {
+  extern __shared__ __align__(16) bf16 xs[];
+  const int p = blockIdx.y;
+  const int e = ids[p];
+  const int cols = GLU ? N / 2 : N;
+  const bf16* xr = x + (size_t)(p / x_div) * ldx;
+  for (int i = threadIdx.x * 8; i < K; i += blockDim.x * 8)
+    *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(xr + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bf16* We = W + (size_t)e * N * K;
+#pragma unroll
+  for (int c = 0; c < GEMV_COLS / 8; ++c) {
+    const int col = blockIdx.x * GEMV_COLS + c * 8 + warp;
+    if (col >= cols) continue;                           // the whole warp
+    float a0 = 0.f, a1 = 0.f;
+    const bf16* w0 = We + (size_t)col * K;
+    const bf16* w1 = We + (size_t)(col + cols) * K;
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xs + k);
+      const uint4 wv = *reinterpret_cast<const uint4*>(w0 + k);
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 xf = __bfloat1622float2(xp[i]), wf = __bfloat1622float2(wp[i]);
+        a0 = fmaf(xf.x, wf.x, a0); a0 = fmaf(xf.y, wf.y, a0);
+      }
+      if (GLU) {
+        const uint4 uv = *reinterpret_cast<const uint4*>(w1 + k);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 xf = __bfloat1622float2(xp[i]), uf = __bfloat1622float2(up[i]);
+          a1 = fmaf(xf.x, uf.x, a1); a1 = fmaf(xf.y, uf.y, a1);
+        }
+      }
+    }
+    a0 = warp_sum(a0);
+    if (GLU) a1 = warp_sum(a1);
+    if (lane == 0) out[(size_t)p * ldo + col] = from_f32<TO>(GLU ? moe_act(a0, act) * a1 : a0);
+  }
+}
+
+// x [*][K] bfloat16: pair p reads row p / x_div.  ids [n]: the expert of every pair.  W [E][N][K] bfloat16.
+// out [n][N] float or bfloat16 (glu: [n][N / 2]), rows in the order of the pairs.  K % 8 == 0, 16-byte aligned rows.
+PHOTON_API int photon_moe_gemv(const void* x, long ldx, int x_div, const int* ids, int n, const void* W, void* out, long ldo,
+                               int out_dtype, int N, int K, int glu, int act, cudaStream_t stream) {
+  if (n <= 0 || N <= 0) return 0;
+  if (K <= 0 || x_div <= 0 || (glu && (N & 1))) return PHOTON_ERR_ARGUMENT;
+  if (K % 8 || ldx % 8 || (uintptr_t)x % 16 || (uintptr_t)W % 16 || n > 65535 || (size_t)K * 2 > 96 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  const int cols = glu ? N / 2 : N;
+  dim3 grid((cols + GEMV_COLS - 1) / GEMV_COLS, n);
+  const size_t smem = (size_t)K * sizeof(bf16);
+#define MOE_GEMV(TO, GLU) do { \
+    if (smem > 48 * 1024) { cudaError_t e_ = cudaFuncSetAttribute(moe_gemv_kernel<TO, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+                            if (e_ != cudaSuccess) return (int)e_; } \
+    moe_gemv_kernel<TO, GLU><<<grid, 256, smem, stream>>>((const bf16*)x, ldx, x_div, ids, (const bf16*)W, (TO*)out, ldo, N, K, act); } while (0)
+  if (out_dtype == PHOTON_BF16) { if (glu) MOE_GEMV(bf16, true); else MOE_GEMV(bf16, false); }
+  else if (out_dtype == PHOTON_F32) { if (glu) MOE_GEMV(float, true); else MOE_GEMV(float, false); }
+  else return PHOTON_ERR_ARGUMENT;
   return launch_status();
 }

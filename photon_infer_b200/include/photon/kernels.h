@@ -85,11 +85,12 @@ PHOTON_EXPORT int photon_rope_table(const float* inv_freq, int half, int count, 
 
 /* ------------------------------------------------------------------ attention.cu (float32 and any even head size) */
 /* Values are dv wide: v_cache [num_pages][n_kv][page_size][dv], out [T][n_q * dv]; v_cache == k_cache (dv <= d): the value
- * of a key is the head of its own row (attention over a cached latent). */
+ * of a key is the head of its own row (attention over a cached latent).  splits > 1: every token's key tiles are shared out
+ * over that many blocks and merged by a second kernel; part: float [T * n_q * splits * (dv + 2)]. */
 PHOTON_EXPORT int photon_paged_attention(const void* q, long q_stride, void* out, long out_stride, int dtype, const void* k_cache,
                            const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                            const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
-                           int window, float scale, int* err, cudaStream_t stream);
+                           int window, float scale, int splits, float* part, int* err, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ latent.cu: attention over a cached latent */
 /* One pass over a token's fused down-projection row down[t] = [query latent (q_rank) | key/value latent (kv_rank) |
@@ -108,6 +109,14 @@ PHOTON_EXPORT int photon_latent_q_rope(const void* q, long q_stride, int dtype, 
  * W [heads][N][K]. */
 PHOTON_EXPORT int photon_head_linear(const void* x, long x_row, long x_head, const void* W, void* out, long o_row, long o_head,
                        int dtype, int M, int heads, int N, int K, cudaStream_t stream);
+
+/* out[p, :] = the cache row of position p < count of the request whose pages are table (cache [num_pages * page_size][width]). */
+PHOTON_EXPORT int photon_gather_rows(const void* cache, int dtype, const int* table, int page_size, int num_pages, int width,
+                       int count, void* out, int* err, cudaStream_t stream);
+/* probs [rows][ldp] = softmax(scale * scores [rows][ld]) over the keys 0 .. first_pos + r / heads of row r, zero beyond,
+ * up to column cols. */
+PHOTON_EXPORT int photon_causal_softmax_rows(const float* scores, long ld, void* probs, long ldp, int dtype, int rows, int heads,
+                               int first_pos, int cols, float scale, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
 /* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), z_t = w_a2 low_t + b_a2, o_t = S^T (q_t *
@@ -135,9 +144,16 @@ PHOTON_EXPORT int photon_moe_tile_rows(void);
 PHOTON_EXPORT int photon_moe_gemm(const void* A, long lda, int dtype, const int* gather, int gather_div, const void* W, void* out,
                     long ldo, int out_dtype, int N, int K, const int* tiles, const int* num_tiles, int max_tiles, int glu,
                     int act, cudaStream_t stream);
-/* out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t]); y [n][H] float. */
-PHOTON_EXPORT int photon_moe_combine(const float* y, long ldy, const int* place, const float* weights, int top,
+/* out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t]); y [n][H] float or bfloat16; place null: row t * top + j. */
+PHOTON_EXPORT int photon_moe_combine(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
                        const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream);
+/* out[r, :] = x[sorted[r] / div, :]: the pairs' input rows in sorted order. */
+PHOTON_EXPORT int photon_moe_gather(const void* x, long ldx, int dtype, const int* sorted, int div, void* out, int n, int H,
+                      cudaStream_t stream);
+/* Few pairs (decode steps), bfloat16: out[p] = W[ids[p]] x[p / x_div], one matrix-vector product per pair, unsorted;
+ * glu as photon_moe_gemm. */
+PHOTON_EXPORT int photon_moe_gemv(const void* x, long ldx, int x_div, const int* ids, int n, const void* W, void* out, long ldo,
+                    int out_dtype, int N, int K, int glu, int act, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_flash.cu (-DHEAD_DIM=d, d % 16 == 0, <= 128; bfloat16) */
 PHOTON_EXPORT int photon_flash_attention_head_dim(void);

@@ -244,12 +244,13 @@ def rope_kv_write(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optio
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float,
-                    err: Optional[torch.Tensor], value_dim: Optional[int] = None) -> None:
+                    err: Optional[torch.Tensor], value_dim: Optional[int] = None, splits: int = 1) -> None:
     """General paged causal attention.  ``q`` is a ``[T, n_q * d]`` view (row stride free),
     ``out [T, n_q * dv]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
     ``max(0, p - window + 1) .. p`` through ``block_table[seq]``.  ``value_dim`` (default ``head_dim``) is the
     width of a value; ``v_cache is k_cache`` means that a key's value is the first ``value_dim`` numbers of
-    its own row (attention over a cached latent)."""
+    its own row (attention over a cached latent).  ``splits`` > 1 shares every token's keys out over that many
+    blocks (for decoded tokens with long contexts; the order of the sums then depends on ``splits``)."""
     _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
     T = q.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
@@ -267,11 +268,16 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         _int32(t, name)
     f = _fn("attention", "photon_paged_attention",
             [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+    splits = max(1, min(int(splits), 64))
+    part = torch.empty(T * n_q * splits * (dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim, dv,
-             k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), _ptr(err), _stream()),
-           "paged_attention")
+             k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), splits, _ptr(part), _ptr(err),
+             _stream()), "paged_attention")
+    if splits > 1:
+        global _launch_count
+        _launch_count += 1
 
 
 _ticket_buffers = {}
@@ -875,6 +881,34 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> Non
              T, heads, N, K, _stream()), "head_linear")
 
 
+def gather_rows(cache: torch.Tensor, table: torch.Tensor, count: int, err: Optional[torch.Tensor]) -> torch.Tensor:
+    """The first ``count`` cached rows of the request whose pages are ``table`` (one row of a block table), as
+    one dense matrix ``[count, width]``; ``cache [pages, 1, page_size, width]``."""
+    _cuda(cache, table, err)
+    _int32(table, "table")
+    pages, _, page_size, width = cache.shape
+    if count > table.numel() * page_size or not cache.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "gather_rows: more rows asked for than the table's pages hold")
+    out = torch.empty((count, width), dtype=cache.dtype, device=cache.device)
+    f = _fn("latent", "photon_gather_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(cache), _dtype_code(cache), _ptr(table), page_size, pages, width, int(count), _ptr(out), _ptr(err), _stream()),
+           "gather_rows")
+    return out
+
+
+def causal_softmax_rows(scores: torch.Tensor, probs: torch.Tensor, heads: int, first_pos: int, scale: float) -> None:
+    """``probs = softmax(scale * scores)`` row by row over the keys each row may see: row ``r`` belongs to the token
+    at position ``first_pos + r // heads`` and sees the keys up to that position; zero beyond."""
+    _cuda(scores, probs)
+    rows, cols = scores.shape
+    if scores.dtype != torch.float32 or scores.stride(1) != 1 or probs.shape != scores.shape or probs.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "causal_softmax_rows: scores float32 [rows, cols], probs of the same shape")
+    f = _fn("latent", "photon_causal_softmax_rows",
+            [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(scores), scores.stride(0), _ptr(probs), probs.stride(0), _dtype_code(probs), rows, int(heads), int(first_pos),
+             cols, float(scale), _stream()), "causal_softmax_rows")
+
+
 # ----------------------------------------------------------------------------- gated linear attention
 
 def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor,
@@ -974,20 +1008,54 @@ def moe_gemm(a: torch.Tensor, gather: Optional[torch.Tensor], gather_div: int, w
              _stream()), "moe_gemm")
 
 
-def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared_out: Optional[torch.Tensor],
+def moe_combine(y: torch.Tensor, place: Optional[torch.Tensor], weights: torch.Tensor, shared_out: Optional[torch.Tensor],
                 out: torch.Tensor) -> None:
-    """``out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t])``, summed in 32-bit in the order of ``j``."""
+    """``out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t])``, summed in 32-bit in the order of ``j``;
+    ``place`` None: the rows of ``y`` stand in the order of the pairs."""
     _cuda(y, place, weights, shared_out, out)
     T, top = weights.shape
     H = y.shape[1]
-    if y.dtype != torch.float32 or y.stride(1) != 1 or out.shape != (T, H) or not out.is_contiguous() \
+    if y.stride(1) != 1 or out.shape != (T, H) or not out.is_contiguous() \
             or (shared_out is not None and (shared_out.shape != (T, H) or not shared_out.is_contiguous()
                                             or shared_out.dtype != out.dtype)):
-        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_combine: y float32 [n, H], out and shared_out contiguous [T, H]")
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_combine: y [n, H], out and shared_out contiguous [T, H]")
     f = _fn("moe", "photon_moe_combine",
-            [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(y), y.stride(0), _ptr(place), _ptr(weights), top, _ptr(shared_out), _ptr(out), _dtype_code(out), T, H,
-             _stream()), "moe_combine")
+            [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), y.stride(0), _dtype_code(y), _ptr(place), _ptr(weights), top, _ptr(shared_out), _ptr(out),
+             _dtype_code(out), T, H, _stream()), "moe_combine")
+
+
+def moe_gather(x: torch.Tensor, srt: torch.Tensor, div: int) -> torch.Tensor:
+    """``out[r] = x[srt[r] // div]``: the pairs' input rows in sorted order."""
+    _cuda(x, srt)
+    n, H = srt.numel(), x.shape[1]
+    out = torch.empty((n, H), dtype=x.dtype, device=x.device)
+    f = _fn("moe", "photon_moe_gather", [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _dtype_code(x), _ptr(srt), int(div), _ptr(out), n, H, _stream()), "moe_gather")
+    return out
+
+
+def moe_gemv_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    K = weight.shape[2]
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.is_contiguous() and K * 2 <= 96 * 1024)
+
+
+def moe_gemv(x: torch.Tensor, x_div: int, ids: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, glu: bool = False,
+             activation: str = "silu") -> None:
+    """A decode step's few (token, choice) pairs: ``out[p] = weight[ids[p]] @ x[p // x_div]``, one matrix-vector
+    product per pair in the order of the pairs, the expert's rows streamed once.  bfloat16 in, bfloat16 or float32 out."""
+    _cuda(x, ids, weight, out)
+    E, N, K = weight.shape
+    n = ids.numel()
+    if not moe_gemv_supported(x, weight) or x.shape[1] != K:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "moe_gemv: bfloat16, K a multiple of 8, aligned rows")
+    if out.shape != (n, N // 2 if glu else N) or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_gemv: out [pairs, N or N / 2]")
+    f = _fn("moe", "photon_moe_gemv",
+            [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), int(x_div), _ptr(ids), n, _ptr(weight), _ptr(out), out.stride(0), _dtype_code(out), N, K,
+             int(glu), ACTIVATIONS[activation], _stream()), "moe_gemv")
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -94,11 +94,65 @@ class LatentAttention(Mixer):
         ops.head_linear(q.view(T, n, d + r)[:, :, :d], self.w_absorb, q_lat[:, :, :kr])
         ops.latent_q_rope(q, n, d, r, self.rot_dims, ctx.positions, self.inv_freq, q_lat, kr)
         o_lat = torch.empty((T, n * kr), dtype=h.dtype, device=h.device)
-        ops.paged_attention(q_lat.view(T, n * self.width), o_lat, cache.k, cache.k, group.block_table, ctx.token_seq,
-                            ctx.positions, n, 1, self.width, self.window, self.scale, ctx.error_flag, value_dim=kr)
+        self.attend(q_lat, o_lat, ctx, cache)
         o = torch.empty((T, n, self.vdim), dtype=h.dtype, device=h.device)
         ops.head_linear(o_lat.view(T, n, kr), self.w_uv, o)
         return project(o.view(T, n * self.vdim), self.w_o)
 
+
+    def attend(self, q_lat: torch.Tensor, o_lat: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        """Decoded tokens, short portions and the float32 run: the paged kernel, whose sums depend only on a token's
+        position.  A long bfloat16 portion: the request's cached rows are gathered into one matrix and attention
+        is three steps per slab of queries, scores = Q C^T (library product, 32-bit out), a causal softmax over the
+        rows, and P C[:, :kv_rank] (library product); a slab ends at the last key its queries may see."""
+        T, n, kr = q_lat.shape[0], self.heads, self.kv_rank
+        group = ctx.groups[cache.group]
+        lens = list(ctx.host_query_lens) or [T]
+        long_rows = [q_lat.dtype == torch.bfloat16 and self.window is None and m >= LIBRARY_MIN_TOKENS for m in lens]
+        t = 0
+        pending = None                                  # a run of neighbouring requests for the paged kernel
+        for s, m in enumerate(lens):
+            if long_rows[s]:
+                if pending is not None:
+                    self._paged(q_lat, o_lat, ctx, cache, pending, t)
+                    pending = None
+                self._dense(q_lat[t:t + m], o_lat[t:t + m], ctx.host_start_positions[s], group.block_table[s], cache, ctx)
+            elif pending is None:
+                pending = t
+            t += m
+        if pending is not None:
+            self._paged(q_lat, o_lat, ctx, cache, pending, T)
+
+    def _paged(self, q_lat, o_lat, ctx, cache, a: int, b: int) -> None:
+        n = self.heads
+        group = ctx.groups[cache.group]
+        splits = 1
+        if q_lat.dtype == torch.bfloat16:
+            # few tokens with long contexts: share every token's key tiles out until the GPU is full (the float32 run keeps
+            # one block per token, whose sums depend on the token's position alone)
+            chunks = -(-n // max(1, min(n, 4096 // self.width)))
+            tiles = -(-max(ctx.max_context_len, 1) // 32)
+            splits = max(1, min(2 * ops.sm_count(q_lat.device) // max(1, (b - a) * chunks), tiles // 2, 64))
+        ops.paged_attention(q_lat[a:b].view(b - a, n * self.width), o_lat[a:b], cache.k, cache.k, group.block_table,
+                            ctx.token_seq[a:b], ctx.positions[a:b], n, 1, self.width, self.window, self.scale,
+                            ctx.error_flag, value_dim=self.kv_rank, splits=splits)
+
+    def _dense(self, q, o, start: int, table: torch.Tensor, cache: LayerCache, ctx: StepContext) -> None:
+        m, n, kr = q.shape[0], self.heads, self.kv_rank
+        rows = ops.gather_rows(cache.k, table, start + m, ctx.error_flag)            # [context, width]
+        slab = max(1, min(m, SCORE_BYTES // (4 * n * (start + m))))
+        for t0 in range(0, m, slab):
+            t1 = min(m, t0 + slab)
+            keys = start + t1                                                          # the last query of the slab sees these
+            scores = torch.mm(q[t0:t1].view((t1 - t0) * n, self.width), rows[:keys].t(), out_dtype=torch.float32)
+            probs = torch.empty(scores.shape, dtype=q.dtype, device=q.device)
+            ops.causal_softmax_rows(scores, probs, n, start + t0, self.scale)
+            torch.mm(probs, rows[:keys, :kr], out=o[t0:t1].view((t1 - t0) * n, kr))
+
+
+#: A request that brings at least this many tokens to a bfloat16 step takes the products-and-softmax path.
+LIBRARY_MIN_TOKENS = 32
+#: Bytes of 32-bit scores held at a time on that path (the queries are cut into slabs that fit).
+SCORE_BYTES = 64 << 20
 
 register_mixer("latent_attention", LatentAttention)

@@ -8,7 +8,9 @@ expert's.  An expert is ``W_down (act(W_gate h) * (W_up h))`` without biases.
 On the device the (token, choice) pairs are sorted by expert without a round trip to the host; two grouped
 products walk the sorted rows (the first gathers its rows of ``h`` and applies the gated activation in its
 epilogue, the second leaves 32-bit rows), and one kernel forms every token's weighted sum in the order of its
-choices and adds the shared expert's output.  The experts' matrices are stacked into ``[E, 2 ff, H]`` and
+choices and adds the shared expert's output.  That is the float32 path and the one for a middling number of
+rows.  A bfloat16 decode step (a handful of pairs) skips the sort and runs one matrix-vector product per pair;
+a bfloat16 step with many rows hands the sorted rows to the library's grouped product.  The experts' matrices are stacked into ``[E, 2 ff, H]`` and
 ``[E, H, ff]`` when loaded.
 """
 from __future__ import annotations
@@ -69,19 +71,41 @@ class MoEFeedForward(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = h.shape
-        ids, weights, counts = ops.moe_route(h, self.w_router, self.b_router, self.top)
-        _, srt, place, tiles, num_tiles, max_tiles = ops.moe_align(ids, counts)
         n = T * self.top
-        act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
-        ops.moe_gemm(h, srt, self.top, self.w_gate_up, act, tiles, num_tiles, max_tiles, glu=True, activation=self.activation)
-        y = torch.empty((n, H), dtype=torch.float32, device=h.device)
-        ops.moe_gemm(act, None, 1, self.w_down, y, tiles, num_tiles, max_tiles)
+        ids, weights, counts = ops.moe_route(h, self.w_router, self.b_router, self.top)
         shared = None
         if self.shared_size:
             shared = project(ops.linear_swiglu(h, self.shared_gate_up, self.shared_activation), self.shared_down)
         out = torch.empty((T, H), dtype=h.dtype, device=h.device)
+        if n <= GEMV_MAX_PAIRS and ops.moe_gemv_supported(h, self.w_gate_up) and self.expert_size % 8 == 0:
+            # a decode step: nothing is sorted, every pair streams its expert's matrices once
+            act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
+            ops.moe_gemv(h, self.top, ids, self.w_gate_up, act, glu=True, activation=self.activation)
+            y = torch.empty((n, H), dtype=torch.float32, device=h.device)
+            ops.moe_gemv(act, 1, ids, self.w_down, y)
+            ops.moe_combine(y, None, weights, shared, out)
+            return out
+        offsets, srt, place, tiles, num_tiles, max_tiles = ops.moe_align(ids, counts)
+        if h.dtype == torch.bfloat16 and n >= GROUPED_LIBRARY_PAIRS and H % 8 == 0 and self.expert_size % 8 == 0:
+            # many bfloat16 rows: the library's grouped product over the rows gathered in sorted order
+            xs = ops.moe_gather(h, srt, self.top)
+            gate_up = torch._grouped_mm(xs, self.w_gate_up.transpose(1, 2), offs=offsets[1:])
+            act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
+            ops.swiglu(gate_up, act, self.activation)
+            y = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=offsets[1:])
+            ops.moe_combine(y, place, weights, shared, out)
+            return out
+        act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
+        ops.moe_gemm(h, srt, self.top, self.w_gate_up, act, tiles, num_tiles, max_tiles, glu=True, activation=self.activation)
+        y = torch.empty((n, H), dtype=torch.float32, device=h.device)
+        ops.moe_gemm(act, None, 1, self.w_down, y, tiles, num_tiles, max_tiles)
         ops.moe_combine(y, place, weights, shared, out)
         return out
 
+
+#: Up to this many (token, choice) pairs a bfloat16 step runs one matrix-vector product per pair.
+GEMV_MAX_PAIRS = 64
+#: From this many pairs on a bfloat16 step hands the sorted rows to the library's grouped product.
+GROUPED_LIBRARY_PAIRS = 256
 
 register_feed_forward("moe", MoEFeedForward)

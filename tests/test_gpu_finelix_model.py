@@ -141,7 +141,8 @@ def test_cuts_agree(session):
             else:
                 scale = float(np.abs(ref).max())
                 per_row = np.abs(other - ref).max(axis=1) / scale
-                assert (per_row > 2e-2).sum() <= max(1, int(0.03 * len(per_row))), \
+                # each side lies within the bfloat16 bound of the oracle, so the two may differ by nearly twice that
+                assert (per_row > 4e-2).sum() <= max(1, int(0.03 * len(per_row))), \
                     f"{label} against whole, request {rid}: worst {float(per_row.max()):.3g}"
 
 

@@ -109,7 +109,8 @@ def _latent_part(dtype, heads=3, dim=16, rot=8, vdim=20, kv_rank=32, q_rank=24, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [dict(), dict(heads=1, dim=24, rot=16, vdim=8, kv_rank=40, q_rank=8, base=1e6)])
-def test_latent_attention_two_requests_in_portions(dtype, shape):
+@pytest.mark.parametrize("long", [False, True])
+def test_latent_attention_two_requests_in_portions(dtype, shape, long):
     """The mixer alone: two requests, each fed in three steps (a long portion, two tokens, single tokens), against
     dense attention over the whole sequence.  Only one row of kv_rank + rot_dim numbers per token is cached."""
     from photon_infer_b200.parts.base import LayerCache
@@ -117,14 +118,15 @@ def test_latent_attention_two_requests_in_portions(dtype, shape):
     spec = att.cache_spec()
     assert (spec.n_kv_heads, spec.head_dim, spec.values) == (1, m["kv_rank"] + m["rot_dim"], False) and att.state_spec() is None
     ps = 4
-    lens = [27, 14]
+    lens = [27, 14] if not long else [125, 60]
     g = torch.Generator().manual_seed(6)
     hs = [torch.randn(L, 48, generator=g).to(dtype) for L in lens]
     want = [plain.latent_attention(w, m, 1e-5, h.double()) for h in hs]
     cache = LayerCache(group=0, k=torch.full((64, 1, ps, spec.head_dim), float("nan"), dtype=dtype, device=DEV))
     got, starts = [[], []], [0, 0]
-    for cut in [(17, 5), (2, 2), (1, 1), (7, 6)]:
-        ctx = _ctx(list(cut), list(starts), ps, dtype)
+    # long: portions of 32 tokens and more take the products-and-softmax path in bfloat16, beside short ones in one step
+    for cut in ([(17, 5), (2, 2), (1, 1), (7, 6)] if not long else [(40, 33), (2, 2), (48, 1), (35, 24)]):
+        ctx = _ctx(list(cut), list(starts), ps, dtype, pages_per_seq=32)
         h = torch.cat([hs[i][starts[i]:starts[i] + cut[i]] for i in range(2)]).to(DEV)
         out = att.forward(h, ctx, cache).float().cpu()
         got[0].append(out[:cut[0]]); got[1].append(out[cut[0]:])
@@ -166,10 +168,12 @@ def test_latent_rows_far_back_at_page_borders_and_at_the_start(dtype, target):
         qq[-1] = qs.reshape(-1)
         out = torch.empty(tokens, heads * dv, dtype=dtype, device=DEV)
         err = torch.zeros(4, dtype=torch.int32, device=DEV)
-        ops.paged_attention(qq.to(dtype).to(DEV), out, cache, cache, bt, i32([0] * tokens), i32(list(range(n - tokens, n))),
-                            heads, 1, width, None, 1.0, err, value_dim=dv)
-        assert err.cpu().tolist()[0] == 0
-        assert rel_err(out[-1].float().cpu().view(heads, dv), want) < (1e-5 if dtype == torch.float32 else 1e-2)
+        for splits in (1, 5, 64):                                                # the keys of a token shared out over blocks
+            out.zero_()
+            ops.paged_attention(qq.to(dtype).to(DEV), out, cache, cache, bt, i32([0] * tokens), i32(list(range(n - tokens, n))),
+                                heads, 1, width, None, 1.0, err, value_dim=dv, splits=splits)
+            assert err.cpu().tolist()[0] == 0
+            assert rel_err(out[-1].float().cpu().view(heads, dv), want) < (1e-5 if dtype == torch.float32 else 1e-2)
     # one row less in the context: the row at the end is not seen by the token before it
     if target == n - 1:
         out = torch.empty(1, heads * dv, dtype=dtype, device=DEV)
