@@ -17,14 +17,21 @@
 #include "common.cuh"
 #include <math.h>
 
-template <typename T, int RPT>
-__global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+// CHUNK false: a block walks all tokens of a request from the state in its slot (see above).
+// CHUNK true (long prompt portions): the block walks ONE chunk of `chunk` tokens of the request that starts at token
+// `first` and brings `count` tokens, from a ZERO state, and leaves what the other two kernels need: the chunk's own
+// outputs o_loc [T][heads][vdim] (no norm yet), the decay from the chunk's start through every token
+// b [T][heads][dim], and the chunk's own end state s_loc [chunks][heads][dim][vdim].
+template <typename T, int RPT, bool CHUNK>
+__global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                                      const T* __restrict__ g, const T* __restrict__ low, long in_stride, int rank,
                                      const T* __restrict__ w_a2, const void* __restrict__ b_a2, int b_bf16,
                                      const void* __restrict__ norm_w, int norm_w_bf16, float eps, float inv_tau,
                                      float qscale, const int* __restrict__ cu_tokens,
                                      const int* __restrict__ state_slots, float* __restrict__ state, int num_slots,
-                                     T* __restrict__ out, long out_stride, int heads, int dim, int vdim, int* err) {
+                                     T* __restrict__ out, long out_stride, int heads, int dim, int vdim, int* err,
+                                     int first, int count, int chunk, float* __restrict__ o_loc,
+                                     float* __restrict__ b_out, float* __restrict__ s_loc, int skip_from) {
   extern __shared__ float sm[];
   const int s = blockIdx.x, h = blockIdx.y;
   const int R = (dim + RPT - 1) / RPT;
@@ -38,14 +45,22 @@ __global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restric
   float* red = part + R * vdim;          // 32
   float* wa = red + 32;                  // dim x (rank + 1): this head's rows of W_a2
   float* ba = wa + dim * (rank + 1);     // dim
-  const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
-  if (t1 <= t0) return;
-  const int slot = state_slots[s];
-  if (slot >= num_slots) {
-    if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
-    return;
+  int t0, t1;
+  float* S = nullptr;
+  if (CHUNK) {
+    t0 = first + s * chunk;
+    t1 = min(first + count, t0 + chunk);
+  } else {
+    t0 = cu_tokens[s]; t1 = cu_tokens[s + 1];
+    if (t1 <= t0 || (skip_from > 0 && t1 - t0 >= skip_from)) return;      // long portions go the chunked way
+    const int slot = state_slots[s];
+    if (slot >= num_slots) {
+      if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
+      return;
+    }
+    if (slot >= 0) S = state + ((size_t)slot * heads + h) * dim * vdim;
   }
-  float* S = slot >= 0 ? state + ((size_t)slot * heads + h) * dim * vdim : nullptr;
+  float cum = 1.f;                                       // CHUNK: the decay of this thread's channel since the chunk's start
   float st[RPT];
   const int row0 = r * RPT;
 #pragma unroll
@@ -55,25 +70,55 @@ __global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restric
   for (int i = tid; i < dim; i += nthreads) ba[i] = load_w(b_a2, b_bf16, (size_t)h * dim + i);
   __syncthreads();
 
-  auto fetch = [&](int t, int buf) {
-    for (int i = tid; i < dim; i += nthreads) {
-      const size_t off = (size_t)t * in_stride + (size_t)h * dim + i;
-      qs[buf * dim + i] = to_f32(q[off]) * qscale;
-      ks[buf * dim + i] = to_f32(k[off]);
-      const T* lw = low + (size_t)t * in_stride;
-      float zz = 0.f;
-      for (int c = 0; c < rank; ++c) zz = fmaf(to_f32(lw[c]), wa[i * (rank + 1) + c], zz);
-      zz += ba[i];
-      const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));          // log(sigmoid(z))
-      as[buf * dim + i] = expf(ls * inv_tau);
+  // Two tokens ahead: the raw q, k and low-rank row of token t + 1 wait in registers while token t is computed, and
+  // become the decayed inputs in shared memory right before they are needed; v and g of the next token likewise.
+  // A block has at least `dim` threads, so thread i < dim owns decay channel i.
+  constexpr int LR = 16;                                 // low-rank values kept in registers; more are read late
+  const bool owner = tid < dim;
+  float rq = 0.f, rk = 0.f, rl[LR];
+  auto load = [&](int t) {
+    if (!owner) return;
+    const size_t off = (size_t)t * in_stride + (size_t)h * dim + tid;
+    rq = to_f32(q[off]);
+    rk = to_f32(k[off]);
+    const T* lw = low + (size_t)t * in_stride;
+#pragma unroll
+    for (int c = 0; c < LR; ++c) rl[c] = c < rank ? to_f32(lw[c]) : 0.f;
+  };
+  auto commit = [&](int t, int buf) {
+    if (!owner) return;
+    const int i = tid;
+    float zz = 0.f;
+#pragma unroll
+    for (int c = 0; c < LR; ++c) if (c < rank) zz = fmaf(rl[c], wa[i * (rank + 1) + c], zz);
+    const T* lw = low + (size_t)t * in_stride;
+    for (int c = LR; c < rank; ++c) zz = fmaf(to_f32(lw[c]), wa[i * (rank + 1) + c], zz);
+    zz += ba[i];
+    const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));            // log(sigmoid(z))
+    const float a = expf(ls * inv_tau);
+    qs[buf * dim + i] = rq * qscale;
+    ks[buf * dim + i] = rk;
+    as[buf * dim + i] = a;
+    if (CHUNK) {
+      cum *= a;
+      b_out[((size_t)t * heads + h) * dim + i] = cum;
     }
   };
-  fetch(t0, 0);
+  load(t0);
+  commit(t0, 0);
+  if (t0 + 1 < t1) load(t0 + 1);
+  float vj = to_f32(v[(size_t)t0 * in_stride + (size_t)h * vdim + j]);
+  float gj = CHUNK ? 0.f : to_f32(g[(size_t)t0 * in_stride + (size_t)h * vdim + j]);
   __syncthreads();
   for (int t = t0; t < t1; ++t) {
     const int buf = (t - t0) & 1;
-    if (t + 1 < t1) fetch(t + 1, buf ^ 1);
-    const float vj = to_f32(v[(size_t)t * in_stride + (size_t)h * vdim + j]);
+    if (t + 1 < t1) commit(t + 1, buf ^ 1);              // its raw values arrived during the last token
+    if (t + 2 < t1) load(t + 2);
+    const float vcur = vj, gcur = gj;
+    if (t + 1 < t1) {
+      vj = to_f32(v[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
+      if (!CHUNK) gj = to_f32(g[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
+    }
     const float* qb = qs + buf * dim + row0;
     const float* kb = ks + buf * dim + row0;
     const float* ab = as + buf * dim + row0;
@@ -81,7 +126,7 @@ __global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restric
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
       if (row0 + i < dim) {
-        st[i] = fmaf(ab[i], st[i], kb[i] * vj);
+        st[i] = fmaf(ab[i], st[i], kb[i] * vcur);
         o = fmaf(st[i], qb[i], o);
       }
     }
@@ -92,13 +137,18 @@ __global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restric
       for (int rr = 0; rr < R; ++rr) tot += part[rr * vdim + j];
       sq = tot * tot;
     }
+    if (CHUNK) {
+      if (r == 0) o_loc[((size_t)t * heads + h) * vdim + j] = tot;
+      __syncthreads();                                   // `part` and the next token's q, k and decay are settled
+      continue;
+    }
     sq = block_sum(sq, red);                               // two barriers inside: `part` and the next token's
     if (r == 0) {                                          // q, k and decay are settled when it returns
       const float inv = 1.0f / sqrtf(sq / (float)vdim + eps);
-      const float gg = to_f32(g[(size_t)t * in_stride + (size_t)h * vdim + j]);
-      out[(size_t)t * out_stride + (size_t)h * vdim + j] = from_f32<T>(tot * inv * wj * (gg / (1.0f + expf(-gg))));
+      out[(size_t)t * out_stride + (size_t)h * vdim + j] = from_f32<T>(tot * inv * wj * (gcur / (1.0f + expf(-gcur))));
     }
   }
+  if (CHUNK) S = s_loc + ((size_t)s * heads + h) * dim * vdim;
   if (S != nullptr && active) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i)
@@ -106,23 +156,94 @@ __global__ void gla_recurrent_kernel(const T* __restrict__ q, const T* __restric
   }
 }
 
-template <typename T, int RPT>
+// The states at the chunks' starts, one (i, j) element per thread, chunk after chunk: start[0] is the state in the
+// request's slot (zero for a negative slot), start[c + 1] = b_end[c] * start[c] + s_loc[c]; s_loc[c] is overwritten
+// with start[c], and the state after the last chunk goes back into the slot.
+__global__ void gla_chunk_scan_kernel(float* __restrict__ s_loc, const float* __restrict__ b, int first, int count,
+                                      int chunk, int chunks, float* __restrict__ state, int slot, int heads, int dim,
+                                      int vdim) {
+  const int h = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= dim * vdim) return;
+  const int i = e / vdim;
+  float* S = slot >= 0 ? state + ((size_t)slot * heads + h) * dim * vdim : nullptr;
+  float cur = S ? S[e] : 0.f;
+  for (int c = 0; c < chunks; ++c) {
+    float* loc = s_loc + ((size_t)c * heads + h) * dim * vdim;
+    const int last = min(first + count, first + (c + 1) * chunk) - 1;
+    const float nxt = fmaf(b[((size_t)last * heads + h) * dim + i], cur, loc[e]);
+    loc[e] = cur;
+    cur = nxt;
+  }
+  if (S) S[e] = cur;
+}
+
+// What the state at the chunk's start adds to every token of the chunk, o_t += sum_i (q_t[i] b_t[i]) start[i][:],
+// then the head's norm and the gate.  One block per (chunk, head); the start state and the decayed queries in shared
+// memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_stride, const float* __restrict__ b,
+                     const float* __restrict__ o_loc, const float* __restrict__ s_start, const void* __restrict__ norm_w,
+                     int norm_w_bf16, float eps, float qscale, int first, int count, int chunk, T* __restrict__ out,
+                     long out_stride, int heads, int dim, int vdim) {
+  extern __shared__ float sm[];
+  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int t0 = first + c * chunk, n = min(first + count, t0 + chunk) - t0;
+  float* Ss = sm;                         // dim x vdim
+  float* qb = Ss + dim * vdim;            // chunk x dim
+  float* os = qb + chunk * dim;           // chunk x vdim
+  const float* src = s_start + ((size_t)c * heads + h) * dim * vdim;
+  for (int e = tid; e < dim * vdim; e += 256) Ss[e] = src[e];
+  for (int e = tid; e < n * dim; e += 256) {
+    const int t = e / dim, i = e - t * dim;
+    qb[e] = to_f32(q[(size_t)(t0 + t) * in_stride + (size_t)h * dim + i]) * qscale * b[((size_t)(t0 + t) * heads + h) * dim + i];
+  }
+  __syncthreads();
+  for (int e = tid; e < n * vdim; e += 256) {
+    const int t = e / vdim, j = e - t * vdim;
+    float a = o_loc[((size_t)(t0 + t) * heads + h) * vdim + j];
+    const float* qt = qb + t * dim;
+    for (int i = 0; i < dim; ++i) a = fmaf(qt[i], Ss[i * vdim + j], a);
+    os[e] = a;
+  }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int t = warp; t < n; t += 8) {
+    float ss = 0.f;
+    for (int j = lane; j < vdim; j += 32) ss += os[t * vdim + j] * os[t * vdim + j];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int j = lane; j < vdim; j += 32) {
+      const float gg = to_f32(g[(size_t)(t0 + t) * in_stride + (size_t)h * vdim + j]);
+      out[(size_t)(t0 + t) * out_stride + (size_t)h * vdim + j] =
+          from_f32<T>(os[t * vdim + j] * inv * load_w(norm_w, norm_w_bf16, j) * (gg / (1.0f + expf(-gg))));
+    }
+  }
+}
+
+template <typename T, int RPT, bool CHUNK>
 static int gla_launch(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
                       int rank, const void* w_a2, const void* b_a2, int b_bf16, const void* norm_w, int norm_w_bf16, float eps, float inv_tau, float qscale,
                       const int* cu_tokens, const int* state_slots, float* state, int num_slots, void* out,
-                      long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream) {
+                      long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream, int first,
+                      int count, int chunk, float* o_loc, float* b_out, float* s_loc, int skip_from) {
   const int R = (dim + RPT - 1) / RPT;
-  if (vdim * R > 1024) return PHOTON_ERR_UNSUPPORTED;
+  if (vdim * R > 512) return PHOTON_ERR_UNSUPPORTED;
   const size_t smem = ((size_t)7 * dim + (size_t)R * vdim + 32 + (size_t)dim * (rank + 1)) * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT, CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  gla_recurrent_kernel<T, RPT><<<dim3(S, heads), dim3((vdim * R + 31) / 32 * 32), smem, stream>>>(
+  int threads = (vdim * R + 31) / 32 * 32;
+  if (threads < dim) threads = (dim + 31) / 32 * 32;                  // thread i < dim owns decay channel i
+  if (threads > 512) return PHOTON_ERR_UNSUPPORTED;
+  gla_recurrent_kernel<T, RPT, CHUNK><<<dim3(S, heads), dim3(threads), smem, stream>>>(
       (const T*)q, (const T*)k, (const T*)v, (const T*)g, (const T*)low, in_stride, rank, (const T*)w_a2, b_a2, b_bf16,
       norm_w, norm_w_bf16, eps, inv_tau,
-      qscale, cu_tokens, state_slots, state, num_slots, (T*)out, out_stride, heads, dim, vdim, err);
+      qscale, cu_tokens, state_slots, state, num_slots, (T*)out, out_stride, heads, dim, vdim, err, first, count, chunk,
+      o_loc, b_out, s_loc, skip_from);
   return launch_status();
 }
 
@@ -134,7 +255,7 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
                                     int b_a2_dtype, const void* norm_w, int norm_w_dtype,
                                     float eps, float tau, float qscale, const int* cu_tokens, const int* state_slots,
                                     float* state, int num_slots, void* out, long out_stride, int S, int heads, int dim,
-                                    int vdim, int* err, cudaStream_t stream) {
+                                    int vdim, int skip_from, int* err, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || rank <= 0 || !(tau > 0.f)) return PHOTON_ERR_ARGUMENT;
   const int bb = b_a2_dtype == PHOTON_BF16;
@@ -146,14 +267,60 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
   while (rpt < 64 && (long)vdim * ((dim + rpt - 1) / rpt) > 512) rpt *= 2;
 #define GLA_ARGS q, k, v, g, low, in_stride, rank, w_a2, b_a2, bb, norm_w, wb, eps, it, qscale, cu_tokens, state_slots, state, \
                  num_slots, out, out_stride, S, heads, dim, vdim, err, stream
+#define GLA_DISPATCH(CHUNK, ...)                                                   \
+  if (dtype == PHOTON_BF16) {                                                      \
+    if (rpt == 8) return gla_launch<bf16, 8, CHUNK>(GLA_ARGS, __VA_ARGS__);        \
+    if (rpt == 16) return gla_launch<bf16, 16, CHUNK>(GLA_ARGS, __VA_ARGS__);      \
+    if (rpt == 32) return gla_launch<bf16, 32, CHUNK>(GLA_ARGS, __VA_ARGS__);      \
+    return gla_launch<bf16, 64, CHUNK>(GLA_ARGS, __VA_ARGS__);                     \
+  }                                                                                \
+  if (rpt == 8) return gla_launch<float, 8, CHUNK>(GLA_ARGS, __VA_ARGS__);         \
+  if (rpt == 16) return gla_launch<float, 16, CHUNK>(GLA_ARGS, __VA_ARGS__);       \
+  if (rpt == 32) return gla_launch<float, 32, CHUNK>(GLA_ARGS, __VA_ARGS__);       \
+  return gla_launch<float, 64, CHUNK>(GLA_ARGS, __VA_ARGS__);
+  GLA_DISPATCH(false, 0, 0, 0, nullptr, nullptr, nullptr, skip_from)
+}
+
+// One long prompt portion (tokens first .. first + count - 1 of the step, state slot `slot`) in chunks that run side by
+// side: every chunk's own recurrence from zero, a scan over the chunks' end states, and the start states' share of the
+// outputs with the norm and the gate.  scratch: float [count * heads * (vdim + dim) + chunks * heads * dim * vdim] with
+// chunks = ceil(count / chunk).  The sums differ from the token-by-token kernel's in their order only.
+PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, const void* g, const void* low,
+                                  long in_stride, int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype,
+                                  const void* norm_w, int norm_w_dtype, float eps, float tau, float qscale, int first,
+                                  int count, int chunk, int slot, float* state, int num_slots, float* scratch, void* out,
+                                  long out_stride, int heads, int dim, int vdim, int* err, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (heads <= 0 || dim <= 0 || vdim <= 0 || rank <= 0 || chunk <= 0 || !(tau > 0.f) || slot >= num_slots) return PHOTON_ERR_ARGUMENT;
+  if (heads > 65535) return PHOTON_ERR_UNSUPPORTED;
+  const int chunks = (count + chunk - 1) / chunk;
+  const size_t smem_out = ((size_t)dim * vdim + (size_t)chunk * (dim + vdim)) * sizeof(float);
+  if (smem_out > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  // the scratch is indexed by the token's place in the step: its three parts are laid out for tokens first ..
+  float* o_loc = scratch - (size_t)first * heads * vdim;
+  float* b = scratch + (size_t)count * heads * vdim - (size_t)first * heads * dim;
+  float* s_loc = scratch + (size_t)count * heads * (vdim + dim);
+  const int wb = norm_w_dtype == PHOTON_BF16, bb = b_a2_dtype == PHOTON_BF16;
+  const float it = 1.0f / tau;
+  int rpt = 8;
+  while (rpt < 64 && (long)vdim * ((dim + rpt - 1) / rpt) > 512) rpt *= 2;
+  const int* cu_tokens = nullptr;
+  const int* state_slots = nullptr;
+  const int S = chunks;
+  int st;
+  { auto run = [&]() -> int { GLA_DISPATCH(true, first, count, chunk, o_loc, b, s_loc, 0) }; st = run(); }
+  if (st != 0) return st;
+  gla_chunk_scan_kernel<<<dim3((dim * vdim + 255) / 256, heads), 256, 0, stream>>>(s_loc, b, first, count, chunk, chunks,
+                                                                                state, slot, heads, dim, vdim);
+  if ((st = launch_status()) != 0) return st;
   if (dtype == PHOTON_BF16) {
-    if (rpt == 8) return gla_launch<bf16, 8>(GLA_ARGS);
-    if (rpt == 16) return gla_launch<bf16, 16>(GLA_ARGS);
-    if (rpt == 32) return gla_launch<bf16, 32>(GLA_ARGS);
-    return gla_launch<bf16, 64>(GLA_ARGS);
+    if (smem_out > 48 * 1024) cudaFuncSetAttribute(gla_chunk_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+    gla_chunk_out_kernel<bf16><<<dim3(chunks, heads), 256, smem_out, stream>>>((const bf16*)q, (const bf16*)g, in_stride, b, o_loc,
+        s_loc, norm_w, wb, eps, qscale, first, count, chunk, (bf16*)out, out_stride, heads, dim, vdim);
+  } else {
+    if (smem_out > 48 * 1024) cudaFuncSetAttribute(gla_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_out);
+    gla_chunk_out_kernel<float><<<dim3(chunks, heads), 256, smem_out, stream>>>((const float*)q, (const float*)g, in_stride, b, o_loc,
+        s_loc, norm_w, wb, eps, qscale, first, count, chunk, (float*)out, out_stride, heads, dim, vdim);
   }
-  if (rpt == 8) return gla_launch<float, 8>(GLA_ARGS);
-  if (rpt == 16) return gla_launch<float, 16>(GLA_ARGS);
-  if (rpt == 32) return gla_launch<float, 32>(GLA_ARGS);
-  return gla_launch<float, 64>(GLA_ARGS);
+  return launch_status();
 }

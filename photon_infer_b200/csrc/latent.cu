@@ -192,11 +192,68 @@ head_linear_kernel(const T* __restrict__ x, long x_row, long x_head, const T* __
   }
 }
 
+// Few bfloat16 rows (decode steps): the rows of x of one head wait in shared memory, every warp streams four rows
+// of W[h] once, 16 bytes per lane and load, against all of them.
+#define HLS_ROWS 8
+__global__ void __launch_bounds__(256)
+head_linear_skinny_kernel(const bf16* __restrict__ x, long x_row, long x_head, const bf16* __restrict__ W,
+                          bf16* __restrict__ out, long o_row, long o_head, int M, int N, int K) {
+  extern __shared__ __align__(16) bf16 xs[];                 // M x K
+  const int h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x * 8; i < M * K; i += blockDim.x * 8) {
+    const int m = i / K, k = i - m * K;
+    *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + (size_t)m * x_row + (size_t)h * x_head + k);
+  }
+  __syncthreads();
+  const bf16* Wh = W + (size_t)h * N * K;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int n = blockIdx.x * 32 + c * 8 + warp;
+    if (n >= N) continue;
+    float acc[HLS_ROWS];
+#pragma unroll
+    for (int m = 0; m < HLS_ROWS; ++m) acc[m] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(Wh + (size_t)n * K + k);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(wp[i]); wf[2 * i] = f.x; wf[2 * i + 1] = f.y; }
+#pragma unroll
+      for (int m = 0; m < HLS_ROWS; ++m) {
+        if (m < M) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + m * K + k);
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(xp[i]);
+            acc[m] = fmaf(f.x, wf[2 * i], acc[m]);
+            acc[m] = fmaf(f.y, wf[2 * i + 1], acc[m]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < HLS_ROWS; ++m) {
+      if (m < M) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) out[(size_t)m * o_row + (size_t)h * o_head + n] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
 // x [M][heads][K] and out [M][heads][N] with row and head strides in elements; W [heads][N][K] contiguous.
 PHOTON_API int photon_head_linear(const void* x, long x_row, long x_head, const void* W, void* out, long o_row,
                                   long o_head, int dtype, int M, int heads, int N, int K, cudaStream_t stream) {
   if (M <= 0 || heads <= 0 || N <= 0) return 0;
   if (K <= 0) return PHOTON_ERR_ARGUMENT;
+  if (dtype == PHOTON_BF16 && M <= HLS_ROWS && K % 8 == 0 && x_row % 8 == 0 && x_head % 8 == 0 && (uintptr_t)x % 16 == 0 &&
+      (uintptr_t)W % 16 == 0 && heads <= 65535 && (size_t)M * K * 2 <= 48 * 1024) {
+    head_linear_skinny_kernel<<<dim3((N + 31) / 32, heads), 256, (size_t)M * K * 2, stream>>>(
+        (const bf16*)x, x_row, x_head, (const bf16*)W, (bf16*)out, o_row, o_head, M, N, K);
+    return launch_status();
+  }
   dim3 grid((N + HL_BN - 1) / HL_BN, (M + HL_BM - 1) / HL_BM, heads);
   if (grid.y > 65535 || grid.z > 65535) return PHOTON_ERR_UNSUPPORTED;
   if (dtype == PHOTON_BF16)

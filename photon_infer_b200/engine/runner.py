@@ -262,7 +262,7 @@ class ModelRunner:
             token_ids=dseg(0), positions=dseg(1), token_seq=dseg(2), cu_tokens=dseg(3),
             context_lens=dseg(4), state_slots=dseg(5), groups=groups,
             host_query_lens=q_lens, host_context_lens=[a + b for a, b in zip(starts, q_lens)],
-            host_start_positions=starts, max_query_len=max(q_lens),
+            host_start_positions=starts, host_state_slots=[int(x) for x in slots[:S]], max_query_len=max(q_lens),
             max_context_len=bound_context or max(a + b for a, b in zip(starts, q_lens)), error_flag=self.error_flag)
         if sampling is not None:
             self._temps = dseg(7 + 2 * G).view(torch.float32)

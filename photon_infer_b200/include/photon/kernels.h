@@ -127,7 +127,16 @@ PHOTON_EXPORT int photon_gla_recurrent(const void* q, const void* k, const void*
                          int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype, const void* norm_w,
                          int norm_w_dtype, float eps, float tau, float qscale, const int* cu_tokens, const int* state_slots,
                          float* state, int num_slots, void* out, long out_stride, int S, int heads, int dim, int vdim,
-                         int* err, cudaStream_t stream);
+                         int skip_from, int* err, cudaStream_t stream);
+/* One long prompt portion (tokens first .. first + count - 1 of the step, state slot `slot`, negative: from zero, nothing
+ * stored) in chunks of `chunk` tokens that run side by side.  scratch: float [count * heads * (vdim + dim) +
+ * ceil(count / chunk) * heads * dim * vdim].  photon_gla_recurrent leaves requests of skip_from tokens or more
+ * (skip_from > 0) to this path. */
+PHOTON_EXPORT int photon_gla_chunked(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
+                       int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype, const void* norm_w,
+                       int norm_w_dtype, float eps, float tau, float qscale, int first, int count, int chunk, int slot,
+                       float* state, int num_slots, float* scratch, void* out, long out_stride, int heads, int dim, int vdim,
+                       int* err, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ moe.cu: routed experts */
 /* Router: logits = Wr h + bias in 32-bit; ids/weights [T][top]: the top experts and the softmax over their logits;

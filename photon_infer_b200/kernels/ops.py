@@ -914,11 +914,12 @@ def causal_softmax_rows(scores: torch.Tensor, probs: torch.Tensor, heads: int, f
 def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor,
                   w_a2: torch.Tensor, b_a2: torch.Tensor, norm_w: torch.Tensor, eps: float, tau: float, qscale: float,
                   cu_tokens: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
-                  num_seqs: int, heads: int, dim: int, vdim: int, err: Optional[torch.Tensor]) -> None:
+                  num_seqs: int, heads: int, dim: int, vdim: int, err: Optional[torch.Tensor], skip_from: int = 0) -> None:
     """The recurrence of gated linear attention over the tokens of a step, request by request, with the decay
     logits ``w_a2 low + b_a2``, the per-head norm and the output gate.  ``q, k [T, heads * dim]``,
     ``v, g [T, heads * vdim]`` and ``low [T, rank]`` are sections of one fused row (same row stride),
-    ``w_a2 [heads * dim, rank]``, ``state [slots, heads, dim, vdim]`` float32, ``out [T, heads * vdim]``."""
+    ``w_a2 [heads * dim, rank]``, ``state [slots, heads, dim, vdim]`` float32, ``out [T, heads * vdim]``.
+    ``skip_from`` > 0: requests that bring that many tokens or more are left alone (``gla_chunked`` runs them)."""
     _cuda(q, k, v, g, low, w_a2, b_a2, norm_w, cu_tokens, state_slots, state, out, err)
     T = q.shape[0]
     rank = low.shape[1]
@@ -937,11 +938,47 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
     f = _fn("gla", "photon_gla_recurrent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
              c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int,
-             c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(low), q.stride(0), _dtype_code(q), rank, _ptr(w_a2), _ptr(b_a2),
              _dtype_code(b_a2), _ptr(norm_w), _dtype_code(norm_w), float(eps), float(tau), float(qscale), _ptr(cu_tokens),
              _ptr(state_slots), _ptr(state), state.shape[0], _ptr(out), out.stride(0), int(num_seqs), heads, dim, vdim,
-             _ptr(err), _stream()), "gla_recurrent")
+             int(skip_from), _ptr(err), _stream()), "gla_recurrent")
+
+
+GLA_CHUNK = 64              # tokens of a chunk of the chunk-parallel recurrence
+
+
+def gla_chunked_supported(dim: int, vdim: int) -> bool:
+    """One decay channel per thread of the chunk kernel, and its shared memory."""
+    rpt = 8
+    while rpt < 64 and vdim * -(-dim // rpt) > 512:
+        rpt *= 2
+    threads = max((vdim * -(-dim // rpt) + 31) // 32 * 32, (dim + 31) // 32 * 32)
+    return threads <= 512 and (dim * vdim + GLA_CHUNK * (dim + vdim)) * 4 <= 200 * 1024
+
+
+def gla_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor, w_a2: torch.Tensor,
+                b_a2: torch.Tensor, norm_w: torch.Tensor, eps: float, tau: float, qscale: float, first: int, count: int,
+                slot: int, state: torch.Tensor, out: torch.Tensor, heads: int, dim: int, vdim: int,
+                err: Optional[torch.Tensor]) -> None:
+    """One long prompt portion (tokens ``first .. first + count - 1`` of the step's rows, state slot ``slot``) with its
+    chunks of ``GLA_CHUNK`` tokens side by side: each chunk's own recurrence from zero, a scan over the chunks' end
+    states, and the start states' share of the outputs with the norm and the gate.  Same tensors as
+    ``gla_recurrent``; the sums differ from its sums in their order only."""
+    _cuda(q, k, v, g, low, w_a2, b_a2, norm_w, state, out, err)
+    rank = low.shape[1]
+    chunks = -(-count // GLA_CHUNK)
+    scratch = torch.empty(count * heads * (vdim + dim) + chunks * heads * dim * vdim, dtype=torch.float32, device=q.device)
+    f = _fn("gla", "photon_gla_chunked",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long,
+             c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(low), q.stride(0), _dtype_code(q), rank, _ptr(w_a2), _ptr(b_a2),
+             _dtype_code(b_a2), _ptr(norm_w), _dtype_code(norm_w), float(eps), float(tau), float(qscale), int(first),
+             int(count), GLA_CHUNK, int(slot), _ptr(state), state.shape[0], _ptr(scratch), _ptr(out), out.stride(0), heads,
+             dim, vdim, _ptr(err), _stream()), "gla_chunked")
+    global _launch_count
+    _launch_count += 2
 
 
 # ----------------------------------------------------------------------------- routed experts

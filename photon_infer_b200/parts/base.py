@@ -119,6 +119,7 @@ class StepContext:
     max_context_len: int = 0
     error_flag: Optional[torch.Tensor] = None   # int32 [4] written by kernels on bad indices
     scratch: Optional[object] = None            # engine.workspace.Workspace
+    host_state_slots: Sequence[int] = ()        # host copy of state_slots
 
 
 # ----------------------------------------------------------------------------- parts

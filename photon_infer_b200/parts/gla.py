@@ -74,11 +74,36 @@ class GatedLinearAttention(Mixer):
         v, g = fused[:, 2 * nd:2 * nd + nv], fused[:, 2 * nd + nv:2 * nd + 2 * nv]
         low = fused[:, 2 * nd + 2 * nv:]
         out = torch.empty((T, nv), dtype=h.dtype, device=h.device)
-        ops.gla_recurrent(q, k, v, g, low, self.w_a2, self.b_a2, self.norm, self.eps, self.tau, self.dim ** -0.5,
-                          ctx.cu_tokens, ctx.state_slots, cache.state, out, ctx.num_seqs, self.heads, self.dim, self.vdim,
-                          ctx.error_flag)
+        # long bfloat16 prompt portions run their chunks side by side; everything else (and the float32 run, whose sums
+        # depend on nothing but the token's place in its request) goes token by token
+        skip = 0
+        lens = list(ctx.host_query_lens)
+        if h.dtype == torch.bfloat16 and lens and max(lens) >= CHUNKED_MIN_TOKENS and ops.gla_chunked_supported(self.dim, self.vdim):
+            skip = CHUNKED_MIN_TOKENS
+            slots = self._host_slots(ctx)
+            t = 0
+            for s, m in enumerate(lens):
+                if m >= skip:
+                    ops.gla_chunked(q, k, v, g, low, self.w_a2, self.b_a2, self.norm, self.eps, self.tau, self.dim ** -0.5,
+                                    t, m, slots[s], cache.state, out, self.heads, self.dim, self.vdim, ctx.error_flag)
+                t += m
+        if skip == 0 or min(lens) < skip:
+            ops.gla_recurrent(q, k, v, g, low, self.w_a2, self.b_a2, self.norm, self.eps, self.tau, self.dim ** -0.5,
+                              ctx.cu_tokens, ctx.state_slots, cache.state, out, ctx.num_seqs, self.heads, self.dim, self.vdim,
+                              ctx.error_flag, skip_from=skip)
         return project(out, self.w_o)
 
+
+    @staticmethod
+    def _host_slots(ctx: StepContext):
+        """The requests' state slots on the host (the chunked path takes a request's slot as a launch argument)."""
+        if ctx.host_state_slots:
+            return list(ctx.host_state_slots)
+        return ctx.state_slots.cpu().tolist()
+
+
+#: A request that brings at least this many tokens to a bfloat16 step runs chunk-parallel.
+CHUNKED_MIN_TOKENS = 128
 
 register_mixer("gla", GatedLinearAttention)
 register_mixer("gla_2", GatedLinearAttention)

@@ -185,10 +185,12 @@ def test_latent_rows_far_back_at_page_borders_and_at_the_start(dtype, target):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(2, 16, 24, 4.0), (1, 72, 40, 16.0), (4, 8, 8, 1.0), (3, 12, 10, 2.0), (2, 128, 64, 8.0)])
-def test_gated_linear_attention_in_portions_and_slots_used_again(dtype, shape):
+@pytest.mark.parametrize("long", [False, True])
+def test_gated_linear_attention_in_portions_and_slots_used_again(dtype, shape, long):
     """Two requests through the mixer in portions (long, two tokens, single tokens), their states in slots 2 and 0 of
     four; then a third request in slot 2 after it was cleared: the state is carried between steps, belongs to the
-    slot and starts at zero."""
+    slot and starts at zero.  ``long``: portions of 128 tokens and more, which in bfloat16 run their chunks of 64 side
+    by side (from a zero state and from a carried one, with a last chunk that is not full), beside short ones."""
     from photon_infer_b200.parts.base import LayerCache
     from photon_infer_b200.parts.registry import create_part
     heads, dim, vdim, tau = shape
@@ -200,7 +202,7 @@ def test_gated_linear_attention_in_portions_and_slots_used_again(dtype, shape):
     state = torch.full((4, heads, dim, vdim), 3.0, dtype=torch.float32, device=DEV)      # stale values of earlier owners
     cache = LayerCache(state=state)
     g = torch.Generator().manual_seed(8)
-    lens = [33, 21]
+    lens = [33, 21] if not long else [341, 150]
     hs = [torch.randn(L, H, generator=g).to(dtype) for L in lens]
     want = [plain.gated_linear_attention(w, m, 1e-5, h.double()) for h in hs]
     tol = 2e-5 if dtype == torch.float32 else 2.5e-2
@@ -208,8 +210,8 @@ def test_gated_linear_attention_in_portions_and_slots_used_again(dtype, shape):
     for s in slots:
         state[s].zero_()                                                             # what the slot pool does at hand-out
     got, starts = [[], []], [0, 0]
-    for cut in [(19, 4), (2, 2), (1, 1), (1, 1), (10, 13)]:
-        ctx = _ctx(list(cut), list(starts), 16, dtype, slots=slots)
+    for cut in ([(19, 4), (2, 2), (1, 1), (1, 1), (10, 13)] if not long else [(170, 4), (2, 2), (1, 128), (168, 16)]):
+        ctx = _ctx(list(cut), list(starts), 16, dtype, slots=slots, pages_per_seq=32)
         h = torch.cat([hs[i][starts[i]:starts[i] + cut[i]] for i in range(2)]).to(DEV)
         out = mixer.forward(h, ctx, cache).float().cpu()
         got[0].append(out[:cut[0]]); got[1].append(out[cut[0]:])
