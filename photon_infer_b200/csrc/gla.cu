@@ -17,13 +17,24 @@
 #include "common.cuh"
 #include <math.h>
 
+// Rows of the state per thread and the block's width: as few rows as keep the block within 256 threads (then a
+// thread may use 255 registers and nothing spills), else within 512.
+static inline void gla_shape(int dim, int vdim, int* rpt, bool* wide) {
+  for (int limit = 256; limit <= 512; limit *= 2) {
+    for (int r = 8; r <= 64; r *= 2) {
+      if ((long)vdim * ((dim + r - 1) / r) <= limit && dim <= limit) { *rpt = r; *wide = limit == 512; return; }
+    }
+  }
+  *rpt = 64; *wide = true;                               // refused by the launcher when it does not fit
+}
+
 // CHUNK false: a block walks all tokens of a request from the state in its slot (see above).
 // CHUNK true (long prompt portions): the block walks ONE chunk of `chunk` tokens of the request that starts at token
 // `first` and brings `count` tokens, from a ZERO state, and leaves what the other two kernels need: the chunk's own
 // outputs o_loc [T][heads][vdim] (no norm yet), the decay from the chunk's start through every token
 // b [T][heads][dim], and the chunk's own end state s_loc [chunks][heads][dim][vdim].
-template <typename T, int RPT, bool CHUNK>
-__global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+template <typename T, int RPT, bool CHUNK, int MAXT>
+__global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                                      const T* __restrict__ g, const T* __restrict__ low, long in_stride, int rank,
                                      const T* __restrict__ w_a2, const void* __restrict__ b_a2, int b_bf16,
                                      const void* __restrict__ norm_w, int norm_w_bf16, float eps, float inv_tau,
@@ -38,10 +49,11 @@ __global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict_
   const int tid = threadIdx.x, nthreads = blockDim.x;                       // a whole number of warps
   const bool active = tid < vdim * R;                                        // the others only meet at barriers
   const int j = active ? tid % vdim : 0, r = active ? tid / vdim : R;
-  float* qs = sm;                        // 2 x dim
-  float* ks = qs + 2 * dim;              // 2 x dim
-  float* as = ks + 2 * dim;              // 2 x dim
-  float* part = as + 2 * dim;            // R x vdim
+  const int dimp = R * RPT;              // rows padded to whole groups: the padding stays zero and adds nothing
+  float* qs = sm;                        // 2 x dimp
+  float* ks = qs + 2 * dimp;             // 2 x dimp
+  float* as = ks + 2 * dimp;             // 2 x dimp
+  float* part = as + 2 * dimp;           // R x vdim
   float* red = part + R * vdim;          // 32
   float* wa = red + 32;                  // dim x (rank + 1): this head's rows of W_a2
   float* ba = wa + dim * (rank + 1);     // dim
@@ -66,6 +78,7 @@ __global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict_
 #pragma unroll
   for (int i = 0; i < RPT; ++i) st[i] = (S != nullptr && active && row0 + i < dim) ? S[(size_t)(row0 + i) * vdim + j] : 0.f;
   const float wj = load_w(norm_w, norm_w_bf16, j);
+  for (int i = tid; i < 6 * dimp; i += nthreads) sm[i] = 0.f;
   for (int i = tid; i < dim * rank; i += nthreads) wa[(i / rank) * (rank + 1) + i % rank] = to_f32(w_a2[(size_t)h * dim * rank + i]);
   for (int i = tid; i < dim; i += nthreads) ba[i] = load_w(b_a2, b_bf16, (size_t)h * dim + i);
   __syncthreads();
@@ -96,9 +109,9 @@ __global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict_
     zz += ba[i];
     const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));            // log(sigmoid(z))
     const float a = expf(ls * inv_tau);
-    qs[buf * dim + i] = rq * qscale;
-    ks[buf * dim + i] = rk;
-    as[buf * dim + i] = a;
+    qs[buf * dimp + i] = rq * qscale;
+    ks[buf * dimp + i] = rk;
+    as[buf * dimp + i] = a;
     if (CHUNK) {
       cum *= a;
       b_out[((size_t)t * heads + h) * dim + i] = cum;
@@ -119,18 +132,28 @@ __global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict_
       vj = to_f32(v[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
       if (!CHUNK) gj = to_f32(g[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
     }
-    const float* qb = qs + buf * dim + row0;
-    const float* kb = ks + buf * dim + row0;
-    const float* ab = as + buf * dim + row0;
     float o = 0.f;
+    if (active) {
+      // a thread's rows lie side by side: four decays, keys and queries per shared-memory read
+      const float4* qb = reinterpret_cast<const float4*>(qs + buf * dimp + row0);
+      const float4* kb = reinterpret_cast<const float4*>(ks + buf * dimp + row0);
+      const float4* ab = reinterpret_cast<const float4*>(as + buf * dimp + row0);
+      float o2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      if (row0 + i < dim) {
-        st[i] = fmaf(ab[i], st[i], kb[i] * vcur);
-        o = fmaf(st[i], qb[i], o);
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 a4 = ab[i], k4 = kb[i], q4 = qb[i];
+        st[4 * i] = fmaf(a4.x, st[4 * i], k4.x * vcur);
+        st[4 * i + 1] = fmaf(a4.y, st[4 * i + 1], k4.y * vcur);
+        st[4 * i + 2] = fmaf(a4.z, st[4 * i + 2], k4.z * vcur);
+        st[4 * i + 3] = fmaf(a4.w, st[4 * i + 3], k4.w * vcur);
+        o = fmaf(st[4 * i], q4.x, o);
+        o2 = fmaf(st[4 * i + 1], q4.y, o2);
+        o = fmaf(st[4 * i + 2], q4.z, o);
+        o2 = fmaf(st[4 * i + 3], q4.w, o2);
       }
+      o += o2;
+      part[r * vdim + j] = o;
     }
-    if (active) part[r * vdim + j] = o;
     __syncthreads();
     float tot = 0.f, sq = 0.f;
     if (r == 0) {
@@ -159,7 +182,7 @@ __global__ void __launch_bounds__(512) gla_recurrent_kernel(const T* __restrict_
 // The states at the chunks' starts, one (i, j) element per thread, chunk after chunk: start[0] is the state in the
 // request's slot (zero for a negative slot), start[c + 1] = b_end[c] * start[c] + s_loc[c]; s_loc[c] is overwritten
 // with start[c], and the state after the last chunk goes back into the slot.
-__global__ void gla_chunk_scan_kernel(float* __restrict__ s_loc, const float* __restrict__ b, int first, int count,
+__global__ void gla_chunk_scan_kernel(float* s_loc, const float* __restrict__ b, int first, int count,
                                       int chunk, int chunks, float* __restrict__ state, int slot, int heads, int dim,
                                       int vdim) {
   const int h = blockIdx.y;
@@ -168,12 +191,31 @@ __global__ void gla_chunk_scan_kernel(float* __restrict__ s_loc, const float* __
   const int i = e / vdim;
   float* S = slot >= 0 ? state + ((size_t)slot * heads + h) * dim * vdim : nullptr;
   float cur = S ? S[e] : 0.f;
-  for (int c = 0; c < chunks; ++c) {
-    float* loc = s_loc + ((size_t)c * heads + h) * dim * vdim;
-    const int last = min(first + count, first + (c + 1) * chunk) - 1;
-    const float nxt = fmaf(b[((size_t)last * heads + h) * dim + i], cur, loc[e]);
-    loc[e] = cur;
-    cur = nxt;
+  auto decay_of = [&](int c) { return b[((size_t)(min(first + count, first + (c + 1) * chunk) - 1) * heads + h) * dim + i]; };
+  auto end_of = [&](int c) { return s_loc[((size_t)c * heads + h) * dim * vdim + e]; };
+  // four chunks' values are on their way before the first of them is used
+  constexpr int AHEAD = 4;
+  float bd[AHEAD], le[AHEAD];
+#pragma unroll
+  for (int u = 0; u < AHEAD; ++u) { bd[u] = u < chunks ? decay_of(u) : 0.f; le[u] = u < chunks ? end_of(u) : 0.f; }
+  for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+    float nb[AHEAD], nl[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      const int c = c0 + AHEAD + u;
+      nb[u] = c < chunks ? decay_of(c) : 0.f;
+      nl[u] = c < chunks ? end_of(c) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      const int c = c0 + u;
+      if (c < chunks) {
+        s_loc[((size_t)c * heads + h) * dim * vdim + e] = cur;
+        cur = fmaf(bd[u], cur, le[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) { bd[u] = nb[u]; le[u] = nl[u]; }
   }
   if (S) S[e] = cur;
 }
@@ -191,21 +233,36 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int t0 = first + c * chunk, n = min(first + count, t0 + chunk) - t0;
   float* Ss = sm;                         // dim x vdim
-  float* qb = Ss + dim * vdim;            // chunk x dim
+  float* qb = Ss + ((dim * vdim + 3) & ~3);   // dim x chunk, 16-byte aligned
   float* os = qb + chunk * dim;           // chunk x vdim
   const float* src = s_start + ((size_t)c * heads + h) * dim * vdim;
   for (int e = tid; e < dim * vdim; e += 256) Ss[e] = src[e];
-  for (int e = tid; e < n * dim; e += 256) {
+  // the decayed queries, transposed: qb[i][t], so that eight tokens of one channel are two 16-byte reads
+  for (int e = tid; e < chunk * dim; e += 256) {
     const int t = e / dim, i = e - t * dim;
-    qb[e] = to_f32(q[(size_t)(t0 + t) * in_stride + (size_t)h * dim + i]) * qscale * b[((size_t)(t0 + t) * heads + h) * dim + i];
+    qb[i * chunk + t] = t < n ? to_f32(q[(size_t)(t0 + t) * in_stride + (size_t)h * dim + i]) * qscale *
+                                    b[((size_t)(t0 + t) * heads + h) * dim + i] : 0.f;
   }
   __syncthreads();
-  for (int e = tid; e < n * vdim; e += 256) {
-    const int t = e / vdim, j = e - t * vdim;
-    float a = o_loc[((size_t)(t0 + t) * heads + h) * vdim + j];
-    const float* qt = qb + t * dim;
-    for (int i = 0; i < dim; ++i) a = fmaf(qt[i], Ss[i * vdim + j], a);
-    os[e] = a;
+  // a thread owns one value column and eight tokens: every element of the start state it reads serves eight sums
+  const int groups = chunk / 8;
+  for (int e = tid; e < groups * vdim; e += 256) {
+    const int tg = e / vdim, j = e - tg * vdim;
+    float a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = 0.f;
+    for (int i = 0; i < dim; ++i) {
+      const float sv = Ss[i * vdim + j];
+      const float4 q0 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8);
+      const float4 q1 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8 + 4);
+      a[0] = fmaf(q0.x, sv, a[0]); a[1] = fmaf(q0.y, sv, a[1]); a[2] = fmaf(q0.z, sv, a[2]); a[3] = fmaf(q0.w, sv, a[3]);
+      a[4] = fmaf(q1.x, sv, a[4]); a[5] = fmaf(q1.y, sv, a[5]); a[6] = fmaf(q1.z, sv, a[6]); a[7] = fmaf(q1.w, sv, a[7]);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int t = tg * 8 + u;
+      if (t < n) os[t * vdim + j] = a[u] + o_loc[((size_t)(t0 + t) * heads + h) * vdim + j];
+    }
   }
   __syncthreads();
   const int warp = tid >> 5, lane = tid & 31;
@@ -222,24 +279,24 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   }
 }
 
-template <typename T, int RPT, bool CHUNK>
+template <typename T, int RPT, bool CHUNK, int MAXT>
 static int gla_launch(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
                       int rank, const void* w_a2, const void* b_a2, int b_bf16, const void* norm_w, int norm_w_bf16, float eps, float inv_tau, float qscale,
                       const int* cu_tokens, const int* state_slots, float* state, int num_slots, void* out,
                       long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream, int first,
                       int count, int chunk, float* o_loc, float* b_out, float* s_loc, int skip_from) {
   const int R = (dim + RPT - 1) / RPT;
-  if (vdim * R > 512) return PHOTON_ERR_UNSUPPORTED;
-  const size_t smem = ((size_t)7 * dim + (size_t)R * vdim + 32 + (size_t)dim * (rank + 1)) * sizeof(float);
+  if (vdim * R > MAXT) return PHOTON_ERR_UNSUPPORTED;
+  const size_t smem = ((size_t)6 * R * RPT + dim + (size_t)R * vdim + 32 + (size_t)dim * (rank + 1)) * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT, CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT, CHUNK, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   int threads = (vdim * R + 31) / 32 * 32;
   if (threads < dim) threads = (dim + 31) / 32 * 32;                  // thread i < dim owns decay channel i
-  if (threads > 512) return PHOTON_ERR_UNSUPPORTED;
-  gla_recurrent_kernel<T, RPT, CHUNK><<<dim3(S, heads), dim3(threads), smem, stream>>>(
+  if (threads > MAXT) return PHOTON_ERR_UNSUPPORTED;
+  gla_recurrent_kernel<T, RPT, CHUNK, MAXT><<<dim3(S, heads), dim3(threads), smem, stream>>>(
       (const T*)q, (const T*)k, (const T*)v, (const T*)g, (const T*)low, in_stride, rank, (const T*)w_a2, b_a2, b_bf16,
       norm_w, norm_w_bf16, eps, inv_tau,
       qscale, cu_tokens, state_slots, state, num_slots, (T*)out, out_stride, heads, dim, vdim, err, first, count, chunk,
@@ -262,22 +319,25 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
   if (heads > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int wb = norm_w_dtype == PHOTON_BF16;
   const float it = 1.0f / tau;
-  // rows of the state per thread: as few as keep the block within 1024 threads
-  int rpt = 8;
-  while (rpt < 64 && (long)vdim * ((dim + rpt - 1) / rpt) > 512) rpt *= 2;
+  int rpt = 0;
+  bool wide = false;
+  gla_shape(dim, vdim, &rpt, &wide);
 #define GLA_ARGS q, k, v, g, low, in_stride, rank, w_a2, b_a2, bb, norm_w, wb, eps, it, qscale, cu_tokens, state_slots, state, \
                  num_slots, out, out_stride, S, heads, dim, vdim, err, stream
-#define GLA_DISPATCH(CHUNK, ...)                                                   \
-  if (dtype == PHOTON_BF16) {                                                      \
-    if (rpt == 8) return gla_launch<bf16, 8, CHUNK>(GLA_ARGS, __VA_ARGS__);        \
-    if (rpt == 16) return gla_launch<bf16, 16, CHUNK>(GLA_ARGS, __VA_ARGS__);      \
-    if (rpt == 32) return gla_launch<bf16, 32, CHUNK>(GLA_ARGS, __VA_ARGS__);      \
-    return gla_launch<bf16, 64, CHUNK>(GLA_ARGS, __VA_ARGS__);                     \
-  }                                                                                \
-  if (rpt == 8) return gla_launch<float, 8, CHUNK>(GLA_ARGS, __VA_ARGS__);         \
-  if (rpt == 16) return gla_launch<float, 16, CHUNK>(GLA_ARGS, __VA_ARGS__);       \
-  if (rpt == 32) return gla_launch<float, 32, CHUNK>(GLA_ARGS, __VA_ARGS__);       \
-  return gla_launch<float, 64, CHUNK>(GLA_ARGS, __VA_ARGS__);
+#define GLA_DISPATCH_T(CHUNK, MAXT, ...)                                                 \
+  if (dtype == PHOTON_BF16) {                                                            \
+    if (rpt == 8) return gla_launch<bf16, 8, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);        \
+    if (rpt == 16) return gla_launch<bf16, 16, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);      \
+    if (rpt == 32) return gla_launch<bf16, 32, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);      \
+    return gla_launch<bf16, 64, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);                     \
+  }                                                                                      \
+  if (rpt == 8) return gla_launch<float, 8, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);         \
+  if (rpt == 16) return gla_launch<float, 16, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);       \
+  if (rpt == 32) return gla_launch<float, 32, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);       \
+  return gla_launch<float, 64, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);
+#define GLA_DISPATCH(CHUNK, ...)                                                         \
+  if (wide) { GLA_DISPATCH_T(CHUNK, 512, __VA_ARGS__) }                                  \
+  GLA_DISPATCH_T(CHUNK, 256, __VA_ARGS__)
   GLA_DISPATCH(false, 0, 0, 0, nullptr, nullptr, nullptr, skip_from)
 }
 
@@ -291,10 +351,11 @@ PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, c
                                   int count, int chunk, int slot, float* state, int num_slots, float* scratch, void* out,
                                   long out_stride, int heads, int dim, int vdim, int* err, cudaStream_t stream) {
   if (count <= 0) return 0;
-  if (heads <= 0 || dim <= 0 || vdim <= 0 || rank <= 0 || chunk <= 0 || !(tau > 0.f) || slot >= num_slots) return PHOTON_ERR_ARGUMENT;
+  if (heads <= 0 || dim <= 0 || vdim <= 0 || rank <= 0 || chunk <= 0 || chunk % 8 || !(tau > 0.f) || slot >= num_slots)
+    return PHOTON_ERR_ARGUMENT;
   if (heads > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int chunks = (count + chunk - 1) / chunk;
-  const size_t smem_out = ((size_t)dim * vdim + (size_t)chunk * (dim + vdim)) * sizeof(float);
+  const size_t smem_out = ((size_t)dim * vdim + 4 + (size_t)chunk * (dim + vdim)) * sizeof(float);
   if (smem_out > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   // the scratch is indexed by the token's place in the step: its three parts are laid out for tokens first ..
   float* o_loc = scratch - (size_t)first * heads * vdim;
@@ -302,8 +363,9 @@ PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, c
   float* s_loc = scratch + (size_t)count * heads * (vdim + dim);
   const int wb = norm_w_dtype == PHOTON_BF16, bb = b_a2_dtype == PHOTON_BF16;
   const float it = 1.0f / tau;
-  int rpt = 8;
-  while (rpt < 64 && (long)vdim * ((dim + rpt - 1) / rpt) > 512) rpt *= 2;
+  int rpt = 0;
+  bool wide = false;
+  gla_shape(dim, vdim, &rpt, &wide);
   const int* cu_tokens = nullptr;
   const int* state_slots = nullptr;
   const int S = chunks;

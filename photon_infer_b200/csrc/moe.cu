@@ -23,15 +23,14 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ Wr,
                                  const void* __restrict__ bias, int bias_bf16, int H, int E, int top,
                                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T_) {
-  extern __shared__ float logits[];                     // warps x E
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T_) return;
-  float* lg = logits + warp * E;
+  extern __shared__ float logits[];                     // E
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int t = blockIdx.x;                              // one block per token, its warps share the experts out
+  float* lg = logits;
   const T* x = h + (size_t)t * h_stride;
   constexpr int V = 16 / sizeof(T);                      // elements of a 16-byte load
   const bool vec = (H % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)Wr % 16 == 0);
-  for (int e = 0; e < E; ++e) {
+  for (int e = warp; e < E; e += nwarp) {
     const T* w = Wr + (size_t)e * H;
     float acc = 0.f;
     if (vec) {
@@ -48,8 +47,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
     acc = warp_sum(acc);
     if (lane == 0) lg[e] = acc + (bias ? load_w(bias, bias_bf16, e) : 0.f);
   }
-  __syncwarp();
-  if (lane == 0) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
     float chosen_max = -INFINITY;
     for (int j = 0; j < top; ++j) {
       int best = -1;
@@ -81,12 +80,12 @@ PHOTON_API int photon_moe_route(const void* h, long h_stride, int dtype, const v
                                 cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || H <= 0) return PHOTON_ERR_ARGUMENT;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float);
+  const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
+  const size_t smem = (size_t)E * sizeof(float);
   if (smem > 48 * 1024) return PHOTON_ERR_UNSUPPORTED;
   cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
-  const int blocks = (T_ + warps - 1) / warps;
+  const int blocks = T_;
   if (dtype == PHOTON_BF16)
     moe_route_kernel<bf16><<<blocks, warps * 32, smem, stream>>>((const bf16*)h, h_stride, (const bf16*)Wr, bias,
                                                                 bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_);

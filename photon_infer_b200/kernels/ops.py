@@ -950,11 +950,8 @@ GLA_CHUNK = 64              # tokens of a chunk of the chunk-parallel recurrence
 
 def gla_chunked_supported(dim: int, vdim: int) -> bool:
     """One decay channel per thread of the chunk kernel, and its shared memory."""
-    rpt = 8
-    while rpt < 64 and vdim * -(-dim // rpt) > 512:
-        rpt *= 2
-    threads = max((vdim * -(-dim // rpt) + 31) // 32 * 32, (dim + 31) // 32 * 32)
-    return threads <= 512 and (dim * vdim + GLA_CHUNK * (dim + vdim)) * 4 <= 200 * 1024
+    fits = any(vdim * -(-dim // rpt) <= 512 for rpt in (8, 16, 32, 64)) and dim <= 512
+    return fits and (dim * vdim + GLA_CHUNK * (dim + vdim)) * 4 <= 200 * 1024
 
 
 def gla_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor, w_a2: torch.Tensor,

@@ -132,7 +132,7 @@ class LatentAttention(Mixer):
             # one block per token, whose sums depend on the token's position alone)
             chunks = -(-n // max(1, min(n, 4096 // self.width)))
             tiles = -(-max(ctx.max_context_len, 1) // 32)
-            splits = max(1, min(2 * ops.sm_count(q_lat.device) // max(1, (b - a) * chunks), tiles // 2, 64))
+            splits = max(1, min(4 * ops.sm_count(q_lat.device) // max(1, (b - a) * chunks), tiles, 64))
         ops.paged_attention(q_lat[a:b].view(b - a, n * self.width), o_lat[a:b], cache.k, cache.k, group.block_table,
                             ctx.token_seq[a:b], ctx.positions[a:b], n, 1, self.width, self.window, self.scale,
                             ctx.error_flag, value_dim=self.kv_rank, splits=splits)
