@@ -19,13 +19,18 @@
 
 // Rows of the state per thread and the block's width: as few rows as keep the block within 256 threads (then a
 // thread may use 255 registers and nothing spills), else within 512.
-static inline void gla_shape(int dim, int vdim, int* rpt, bool* wide) {
-  for (int limit = 256; limit <= 512; limit *= 2) {
+static inline void gla_shape(int dim, int vdim, int* rpt, int* maxt) {
+  static int forced = -1;                                // PHOTON_GLA_THREADS=256|512|1024 picks the width (for measurements)
+  if (forced < 0) { const char* e = getenv("PHOTON_GLA_THREADS"); forced = e ? atoi(e) : 0; }
+  // as many threads as the state has elements for, eight rows a thread at least, 1024 at most: the step of the
+  // recurrence is a chain of short dependent pieces, and what hides their latency is the number of warps
+  for (int limit = forced ? forced : 1024; limit >= 256; limit /= 2) {
     for (int r = 8; r <= 64; r *= 2) {
-      if ((long)vdim * ((dim + r - 1) / r) <= limit && dim <= limit) { *rpt = r; *wide = limit == 512; return; }
+      if ((long)vdim * ((dim + r - 1) / r) <= limit && dim <= limit) { *rpt = r; *maxt = limit; return; }
     }
+    if (forced) break;
   }
-  *rpt = 64; *wide = true;                               // refused by the launcher when it does not fit
+  *rpt = 64; *maxt = 1024;                               // refused by the launcher when it does not fit
 }
 
 // CHUNK false: a block walks all tokens of a request from the state in its slot (see above).
@@ -86,7 +91,7 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
   // Two tokens ahead: the raw q, k and low-rank row of token t + 1 wait in registers while token t is computed, and
   // become the decayed inputs in shared memory right before they are needed; v and g of the next token likewise.
   // A block has at least `dim` threads, so thread i < dim owns decay channel i.
-  constexpr int LR = 16;                                 // low-rank values kept in registers; more are read late
+  constexpr int LR = MAXT >= 1024 ? 8 : 16;              // low-rank values kept in registers; more are read late
   const bool owner = tid < dim;
   float rq = 0.f, rk = 0.f, rl[LR];
   auto load = [&](int t) {
@@ -179,6 +184,131 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
   }
 }
 
+// ---------------------------------------------------------------- one chunk of a long portion, from a zero state
+// Everything the chunk needs is brought into shared memory at once (decayed inputs of all its tokens, formed side
+// by side), the walk over its tokens then touches no global memory but its results and meets no barrier: thread
+// j * RP + r keeps rows r * RPT .. of column j, and the RP partial sums of a column lie in neighbouring lanes and
+// meet by shuffles.  Leaves the chunk's own outputs o_loc [T][heads][vdim] (no norm yet), the decay from the chunk's
+// start through every token b [T][heads][dim], and the chunk's end state s_loc [chunks][heads][dim][vdim].
+template <typename T, int RPT>
+__global__ void __launch_bounds__(512)
+gla_chunk_local_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                       const T* __restrict__ low, long in_stride, int rank, const T* __restrict__ w_a2,
+                       const void* __restrict__ b_a2, int b_bf16, float inv_tau, float qscale, int first, int count,
+                       int chunk, float* __restrict__ o_loc, float* __restrict__ b_out, float* __restrict__ s_loc,
+                       int heads, int dim, int vdim, int RP) {
+  extern __shared__ __align__(16) float sm[];
+  const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthreads = blockDim.x;
+  const int R = (dim + RPT - 1) / RPT;
+  const int gs = RPT + 4;                  // a row group's stride: groups start in different banks
+  const int dimp = R * gs;
+  const int t0 = first + c * chunk, n = min(first + count, t0 + chunk) - t0;
+  float* qf = sm;                          // chunk x dimp
+  float* kf = qf + chunk * dimp;
+  float* af = kf + chunk * dimp;
+  float* vf = af + chunk * dimp;           // chunk x vdim
+  float* wa = vf + chunk * vdim;           // dim x (rank + 1)
+  float* ba = wa + dim * (rank + 1);       // dim
+  for (int i = tid; i < dim * rank; i += nthreads) wa[(i / rank) * (rank + 1) + i % rank] = to_f32(w_a2[(size_t)h * dim * rank + i]);
+  for (int i = tid; i < dim; i += nthreads) ba[i] = load_w(b_a2, b_bf16, (size_t)h * dim + i);
+  for (int i = tid; i < 3 * chunk * dimp; i += nthreads) sm[i] = 0.f;
+  __syncthreads();
+  for (int e = tid; e < n * dim; e += nthreads) {
+    const int t = e / dim, i = e - t * dim;
+    const size_t off = (size_t)(t0 + t) * in_stride + (size_t)h * dim + i;
+    const T* lw = low + (size_t)(t0 + t) * in_stride;
+    float zz = 0.f;
+    for (int r = 0; r < rank; ++r) zz = fmaf(to_f32(lw[r]), wa[i * (rank + 1) + r], zz);
+    zz += ba[i];
+    const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));            // log(sigmoid(z))
+    const int at = t * dimp + (i / RPT) * gs + i % RPT;
+    qf[at] = to_f32(q[off]) * qscale;
+    kf[at] = to_f32(k[off]);
+    af[at] = expf(ls * inv_tau);
+  }
+  for (int e = tid; e < n * vdim; e += nthreads) {
+    const int t = e / vdim, j = e - t * vdim;
+    vf[e] = to_f32(v[(size_t)(t0 + t) * in_stride + (size_t)h * vdim + j]);
+  }
+  __syncthreads();
+  if (tid < dim) {                          // the decay since the chunk's start, channel by channel
+    float cum = 1.f;
+    const int at = (tid / RPT) * gs + tid % RPT;
+    for (int t = 0; t < n; ++t) {
+      cum *= af[t * dimp + at];
+      b_out[((size_t)(t0 + t) * heads + h) * dim + tid] = cum;
+    }
+  }
+  const int j = tid / RP, r = tid % RP;
+  const bool active = j < vdim && r < R;
+  float st[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) st[i] = 0.f;
+  const int g0 = (r < R ? r : 0) * gs;
+  for (int t = 0; t < n; ++t) {
+    float o = 0.f, o2 = 0.f;
+    if (active) {
+      const float vcur = vf[t * vdim + j];
+      const float4* qb = reinterpret_cast<const float4*>(qf + t * dimp + g0);
+      const float4* kb = reinterpret_cast<const float4*>(kf + t * dimp + g0);
+      const float4* ab = reinterpret_cast<const float4*>(af + t * dimp + g0);
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 a4 = ab[i], k4 = kb[i], q4 = qb[i];
+        st[4 * i] = fmaf(a4.x, st[4 * i], k4.x * vcur);
+        st[4 * i + 1] = fmaf(a4.y, st[4 * i + 1], k4.y * vcur);
+        st[4 * i + 2] = fmaf(a4.z, st[4 * i + 2], k4.z * vcur);
+        st[4 * i + 3] = fmaf(a4.w, st[4 * i + 3], k4.w * vcur);
+        o = fmaf(st[4 * i], q4.x, o);
+        o2 = fmaf(st[4 * i + 1], q4.y, o2);
+        o = fmaf(st[4 * i + 2], q4.z, o);
+        o2 = fmaf(st[4 * i + 3], q4.w, o2);
+      }
+      o += o2;
+    }
+    for (int d = 1; d < RP; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);   // RP lanes of a column, fixed order
+    if (active && r == 0) o_loc[((size_t)(t0 + t) * heads + h) * vdim + j] = o;
+  }
+  if (active) {
+    float* S = s_loc + ((size_t)c * heads + h) * dim * vdim;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i)
+      if (r * RPT + i < dim) S[(size_t)(r * RPT + i) * vdim + j] = st[i];
+  }
+}
+
+template <typename T, int RPT>
+static int gla_chunk_local_launch(const void* q, const void* k, const void* v, const void* low, long in_stride, int rank,
+                                  const void* w_a2, const void* b_a2, int bb, float it, float qscale, int first, int count,
+                                  int chunk, float* o_loc, float* b, float* s_loc, int heads, int dim, int vdim, int rp,
+                                  int chunks, cudaStream_t stream) {
+  const int R = (dim + RPT - 1) / RPT;
+  const size_t smem = ((size_t)3 * chunk * R * (RPT + 4) + (size_t)chunk * vdim + (size_t)dim * (rank + 2)) * sizeof(float);
+  int threads = (vdim * rp + 31) / 32 * 32;
+  if (threads < dim) threads = (dim + 31) / 32 * 32;
+  if (threads > 512 || smem > 220 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gla_chunk_local_kernel<T, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  gla_chunk_local_kernel<T, RPT><<<dim3(chunks, heads), threads, smem, stream>>>(
+      (const T*)q, (const T*)k, (const T*)v, (const T*)low, in_stride, rank, (const T*)w_a2, b_a2, bb, it, qscale, first,
+      count, chunk, o_loc, b, s_loc, heads, dim, vdim, rp);
+  return launch_status();
+}
+
+// Rows per thread of the chunk kernel: the fewest with which the block (columns x row groups, the groups rounded up to a
+// power of two so that they meet by shuffles) stays within 512 threads.  0: no shape fits.
+static inline int gla_chunk_rows(int dim, int vdim, int* rp) {
+  for (int r = 8; r <= 64; r *= 2) {
+    const int R = (dim + r - 1) / r;
+    int p = 1;
+    while (p < R) p <<= 1;
+    if (p <= 32 && (long)vdim * p <= 512 && dim <= 512) { *rp = p; return r; }
+  }
+  return 0;
+}
+
 // The states at the chunks' starts, one (i, j) element per thread, chunk after chunk: start[0] is the state in the
 // request's slot (zero for a negative slot), start[c + 1] = b_end[c] * start[c] + s_loc[c]; s_loc[c] is overwritten
 // with start[c], and the state after the last chunk goes back into the slot.
@@ -236,7 +366,11 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   float* qb = Ss + ((dim * vdim + 3) & ~3);   // dim x chunk, 16-byte aligned
   float* os = qb + chunk * dim;           // chunk x vdim
   const float* src = s_start + ((size_t)c * heads + h) * dim * vdim;
-  for (int e = tid; e < dim * vdim; e += 256) Ss[e] = src[e];
+  if ((dim * vdim) % 4 == 0) {
+    for (int e = tid; e < dim * vdim / 4; e += 256) reinterpret_cast<float4*>(Ss)[e] = reinterpret_cast<const float4*>(src)[e];
+  } else {
+    for (int e = tid; e < dim * vdim; e += 256) Ss[e] = src[e];
+  }
   // the decayed queries, transposed: qb[i][t], so that eight tokens of one channel are two 16-byte reads
   for (int e = tid; e < chunk * dim; e += 256) {
     const int t = e / dim, i = e - t * dim;
@@ -244,24 +378,41 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
                                     b[((size_t)(t0 + t) * heads + h) * dim + i] : 0.f;
   }
   __syncthreads();
-  // a thread owns one value column and eight tokens: every element of the start state it reads serves eight sums
-  const int groups = chunk / 8;
-  for (int e = tid; e < groups * vdim; e += 256) {
-    const int tg = e / vdim, j = e - tg * vdim;
-    float a[8];
+  // a thread owns four value columns and eight tokens: three 16-byte reads of shared memory serve 32 multiply-adds
+  const int groups = chunk / 8, quads = (vdim + 3) / 4;
+  const bool vec4 = (vdim & 3) == 0;
+  for (int e = tid; e < groups * quads; e += 256) {
+    const int tg = e / quads, j = (e - tg * quads) * 4;
+    float a[8][4];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) a[u] = 0.f;
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int w = 0; w < 4; ++w) a[u][w] = 0.f;
     for (int i = 0; i < dim; ++i) {
-      const float sv = Ss[i * vdim + j];
+      float sv[4];
+      if (vec4) {
+        const float4 s4 = *reinterpret_cast<const float4*>(Ss + i * vdim + j);
+        sv[0] = s4.x; sv[1] = s4.y; sv[2] = s4.z; sv[3] = s4.w;
+      } else {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) sv[w] = j + w < vdim ? Ss[i * vdim + j + w] : 0.f;
+      }
       const float4 q0 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8);
       const float4 q1 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8 + 4);
-      a[0] = fmaf(q0.x, sv, a[0]); a[1] = fmaf(q0.y, sv, a[1]); a[2] = fmaf(q0.z, sv, a[2]); a[3] = fmaf(q0.w, sv, a[3]);
-      a[4] = fmaf(q1.x, sv, a[4]); a[5] = fmaf(q1.y, sv, a[5]); a[6] = fmaf(q1.z, sv, a[6]); a[7] = fmaf(q1.w, sv, a[7]);
+      const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) a[u][w] = fmaf(qv[u], sv[w], a[u][w]);
     }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int t = tg * 8 + u;
-      if (t < n) os[t * vdim + j] = a[u] + o_loc[((size_t)(t0 + t) * heads + h) * vdim + j];
+      if (t < n) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          if (j + w < vdim) os[t * vdim + j + w] = a[u][w] + o_loc[((size_t)(t0 + t) * heads + h) * vdim + j + w];
+      }
     }
   }
   __syncthreads();
@@ -319,9 +470,8 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
   if (heads > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int wb = norm_w_dtype == PHOTON_BF16;
   const float it = 1.0f / tau;
-  int rpt = 0;
-  bool wide = false;
-  gla_shape(dim, vdim, &rpt, &wide);
+  int rpt = 0, maxt = 256;
+  gla_shape(dim, vdim, &rpt, &maxt);
 #define GLA_ARGS q, k, v, g, low, in_stride, rank, w_a2, b_a2, bb, norm_w, wb, eps, it, qscale, cu_tokens, state_slots, state, \
                  num_slots, out, out_stride, S, heads, dim, vdim, err, stream
 #define GLA_DISPATCH_T(CHUNK, MAXT, ...)                                                 \
@@ -336,7 +486,8 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
   if (rpt == 32) return gla_launch<float, 32, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);       \
   return gla_launch<float, 64, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);
 #define GLA_DISPATCH(CHUNK, ...)                                                         \
-  if (wide) { GLA_DISPATCH_T(CHUNK, 512, __VA_ARGS__) }                                  \
+  if (maxt == 1024) { GLA_DISPATCH_T(CHUNK, 1024, __VA_ARGS__) }                         \
+  if (maxt == 512) { GLA_DISPATCH_T(CHUNK, 512, __VA_ARGS__) }                           \
   GLA_DISPATCH_T(CHUNK, 256, __VA_ARGS__)
   GLA_DISPATCH(false, 0, 0, 0, nullptr, nullptr, nullptr, skip_from)
 }
@@ -363,14 +514,14 @@ PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, c
   float* s_loc = scratch + (size_t)count * heads * (vdim + dim);
   const int wb = norm_w_dtype == PHOTON_BF16, bb = b_a2_dtype == PHOTON_BF16;
   const float it = 1.0f / tau;
-  int rpt = 0;
-  bool wide = false;
-  gla_shape(dim, vdim, &rpt, &wide);
-  const int* cu_tokens = nullptr;
-  const int* state_slots = nullptr;
-  const int S = chunks;
+  int rp = 1;
+  const int rows = gla_chunk_rows(dim, vdim, &rp);
+  if (rows == 0) return PHOTON_ERR_UNSUPPORTED;
   int st;
-  { auto run = [&]() -> int { GLA_DISPATCH(true, first, count, chunk, o_loc, b, s_loc, 0) }; st = run(); }
+#define GLA_LOCAL(T, RPT) gla_chunk_local_launch<T, RPT>(q, k, v, low, in_stride, rank, w_a2, b_a2, bb, it, qscale, first, \
+                                                         count, chunk, o_loc, b, s_loc, heads, dim, vdim, rp, chunks, stream)
+  if (dtype == PHOTON_BF16) st = rows == 8 ? GLA_LOCAL(bf16, 8) : rows == 16 ? GLA_LOCAL(bf16, 16) : rows == 32 ? GLA_LOCAL(bf16, 32) : GLA_LOCAL(bf16, 64);
+  else st = rows == 8 ? GLA_LOCAL(float, 8) : rows == 16 ? GLA_LOCAL(float, 16) : rows == 32 ? GLA_LOCAL(float, 32) : GLA_LOCAL(float, 64);
   if (st != 0) return st;
   gla_chunk_scan_kernel<<<dim3((dim * vdim + 255) / 256, heads), 256, 0, stream>>>(s_loc, b, first, count, chunk, chunks,
                                                                                 state, slot, heads, dim, vdim);

@@ -948,10 +948,19 @@ def gla_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
 GLA_CHUNK = 64              # tokens of a chunk of the chunk-parallel recurrence
 
 
-def gla_chunked_supported(dim: int, vdim: int) -> bool:
-    """One decay channel per thread of the chunk kernel, and its shared memory."""
-    fits = any(vdim * -(-dim // rpt) <= 512 for rpt in (8, 16, 32, 64)) and dim <= 512
-    return fits and (dim * vdim + GLA_CHUNK * (dim + vdim)) * 4 <= 200 * 1024
+def gla_chunked_supported(dim: int, vdim: int, rank: int = 64) -> bool:
+    """A block shape of the chunk kernel exists (columns x row groups within 512 threads, the groups a power of two),
+    and the shared memory of the two chunk kernels fits."""
+    for rpt in (8, 16, 32, 64):
+        groups = -(-dim // rpt)
+        p = 1
+        while p < groups:
+            p *= 2
+        if p <= 32 and vdim * p <= 512 and dim <= 512:
+            local = (3 * GLA_CHUNK * groups * (rpt + 4) + GLA_CHUNK * vdim + dim * (rank + 2)) * 4
+            out = (dim * vdim + 4 + GLA_CHUNK * (dim + vdim)) * 4
+            return local <= 220 * 1024 and out <= 200 * 1024
+    return False
 
 
 def gla_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, low: torch.Tensor, w_a2: torch.Tensor,

@@ -78,7 +78,7 @@ class GatedLinearAttention(Mixer):
         # depend on nothing but the token's place in its request) goes token by token
         skip = 0
         lens = list(ctx.host_query_lens)
-        if h.dtype == torch.bfloat16 and lens and max(lens) >= CHUNKED_MIN_TOKENS and ops.gla_chunked_supported(self.dim, self.vdim):
+        if h.dtype == torch.bfloat16 and lens and max(lens) >= CHUNKED_MIN_TOKENS and ops.gla_chunked_supported(self.dim, self.vdim, self.decay_rank or 64):
             skip = CHUNKED_MIN_TOKENS
             slots = self._host_slots(ctx)
             t = 0
