@@ -20,25 +20,18 @@
 // Rows of the state per thread and the block's width: as few rows as keep the block within 256 threads (then a
 // thread may use 255 registers and nothing spills), else within 512.
 static inline void gla_shape(int dim, int vdim, int* rpt, int* maxt) {
-  static int forced = -1;                                // PHOTON_GLA_THREADS=256|512|1024 picks the width (for measurements)
-  if (forced < 0) { const char* e = getenv("PHOTON_GLA_THREADS"); forced = e ? atoi(e) : 0; }
-  // as many threads as the state has elements for, eight rows a thread at least, 1024 at most: the step of the
-  // recurrence is a chain of short dependent pieces, and what hides their latency is the number of warps
-  for (int limit = forced ? forced : 1024; limit >= 256; limit /= 2) {
+  // the narrowest block that holds the state with at most 64 rows a thread: 256 threads may use 255 registers each
+  // and nothing spills.  Measured at heads of 128 x 128: blocks of 256, 512 and 1024 threads take the same time.
+  for (int limit = 256; limit <= 1024; limit *= 2) {
     for (int r = 8; r <= 64; r *= 2) {
       if ((long)vdim * ((dim + r - 1) / r) <= limit && dim <= limit) { *rpt = r; *maxt = limit; return; }
     }
-    if (forced) break;
   }
   *rpt = 64; *maxt = 1024;                               // refused by the launcher when it does not fit
 }
 
-// CHUNK false: a block walks all tokens of a request from the state in its slot (see above).
-// CHUNK true (long prompt portions): the block walks ONE chunk of `chunk` tokens of the request that starts at token
-// `first` and brings `count` tokens, from a ZERO state, and leaves what the other two kernels need: the chunk's own
-// outputs o_loc [T][heads][vdim] (no norm yet), the decay from the chunk's start through every token
-// b [T][heads][dim], and the chunk's own end state s_loc [chunks][heads][dim][vdim].
-template <typename T, int RPT, bool CHUNK, int MAXT>
+// skip_from > 0: requests that bring that many tokens or more are left to the chunked kernels below.
+template <typename T, int RPT, int MAXT>
 __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                                      const T* __restrict__ g, const T* __restrict__ low, long in_stride, int rank,
                                      const T* __restrict__ w_a2, const void* __restrict__ b_a2, int b_bf16,
@@ -46,8 +39,7 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
                                      float qscale, const int* __restrict__ cu_tokens,
                                      const int* __restrict__ state_slots, float* __restrict__ state, int num_slots,
                                      T* __restrict__ out, long out_stride, int heads, int dim, int vdim, int* err,
-                                     int first, int count, int chunk, float* __restrict__ o_loc,
-                                     float* __restrict__ b_out, float* __restrict__ s_loc, int skip_from) {
+                                     int skip_from) {
   extern __shared__ float sm[];
   const int s = blockIdx.x, h = blockIdx.y;
   const int R = (dim + RPT - 1) / RPT;
@@ -62,22 +54,14 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
   float* red = part + R * vdim;          // 32
   float* wa = red + 32;                  // dim x (rank + 1): this head's rows of W_a2
   float* ba = wa + dim * (rank + 1);     // dim
-  int t0, t1;
-  float* S = nullptr;
-  if (CHUNK) {
-    t0 = first + s * chunk;
-    t1 = min(first + count, t0 + chunk);
-  } else {
-    t0 = cu_tokens[s]; t1 = cu_tokens[s + 1];
-    if (t1 <= t0 || (skip_from > 0 && t1 - t0 >= skip_from)) return;      // long portions go the chunked way
-    const int slot = state_slots[s];
-    if (slot >= num_slots) {
-      if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
-      return;
-    }
-    if (slot >= 0) S = state + ((size_t)slot * heads + h) * dim * vdim;
+  const int t0 = cu_tokens[s], t1 = cu_tokens[s + 1];
+  if (t1 <= t0 || (skip_from > 0 && t1 - t0 >= skip_from)) return;        // long portions go the chunked way
+  const int slot = state_slots[s];
+  if (slot >= num_slots) {
+    if (tid == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t0, slot, num_slots);
+    return;
   }
-  float cum = 1.f;                                       // CHUNK: the decay of this thread's channel since the chunk's start
+  float* S = slot >= 0 ? state + ((size_t)slot * heads + h) * dim * vdim : nullptr;
   float st[RPT];
   const int row0 = r * RPT;
 #pragma unroll
@@ -117,16 +101,12 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
     qs[buf * dimp + i] = rq * qscale;
     ks[buf * dimp + i] = rk;
     as[buf * dimp + i] = a;
-    if (CHUNK) {
-      cum *= a;
-      b_out[((size_t)t * heads + h) * dim + i] = cum;
-    }
   };
   load(t0);
   commit(t0, 0);
   if (t0 + 1 < t1) load(t0 + 1);
   float vj = to_f32(v[(size_t)t0 * in_stride + (size_t)h * vdim + j]);
-  float gj = CHUNK ? 0.f : to_f32(g[(size_t)t0 * in_stride + (size_t)h * vdim + j]);
+  float gj = to_f32(g[(size_t)t0 * in_stride + (size_t)h * vdim + j]);
   __syncthreads();
   for (int t = t0; t < t1; ++t) {
     const int buf = (t - t0) & 1;
@@ -135,7 +115,7 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
     const float vcur = vj, gcur = gj;
     if (t + 1 < t1) {
       vj = to_f32(v[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
-      if (!CHUNK) gj = to_f32(g[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
+      gj = to_f32(g[(size_t)(t + 1) * in_stride + (size_t)h * vdim + j]);
     }
     float o = 0.f;
     if (active) {
@@ -165,18 +145,12 @@ __global__ void __launch_bounds__(MAXT) gla_recurrent_kernel(const T* __restrict
       for (int rr = 0; rr < R; ++rr) tot += part[rr * vdim + j];
       sq = tot * tot;
     }
-    if (CHUNK) {
-      if (r == 0) o_loc[((size_t)t * heads + h) * vdim + j] = tot;
-      __syncthreads();                                   // `part` and the next token's q, k and decay are settled
-      continue;
-    }
     sq = block_sum(sq, red);                               // two barriers inside: `part` and the next token's
     if (r == 0) {                                          // q, k and decay are settled when it returns
       const float inv = 1.0f / sqrtf(sq / (float)vdim + eps);
       out[(size_t)t * out_stride + (size_t)h * vdim + j] = from_f32<T>(tot * inv * wj * (gcur / (1.0f + expf(-gcur))));
     }
   }
-  if (CHUNK) S = s_loc + ((size_t)s * heads + h) * dim * vdim;
   if (S != nullptr && active) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i)
@@ -430,28 +404,26 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   }
 }
 
-template <typename T, int RPT, bool CHUNK, int MAXT>
+template <typename T, int RPT, int MAXT>
 static int gla_launch(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
                       int rank, const void* w_a2, const void* b_a2, int b_bf16, const void* norm_w, int norm_w_bf16, float eps, float inv_tau, float qscale,
                       const int* cu_tokens, const int* state_slots, float* state, int num_slots, void* out,
-                      long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream, int first,
-                      int count, int chunk, float* o_loc, float* b_out, float* s_loc, int skip_from) {
+                      long out_stride, int S, int heads, int dim, int vdim, int* err, cudaStream_t stream, int skip_from) {
   const int R = (dim + RPT - 1) / RPT;
   if (vdim * R > MAXT) return PHOTON_ERR_UNSUPPORTED;
   const size_t smem = ((size_t)6 * R * RPT + dim + (size_t)R * vdim + 32 + (size_t)dim * (rank + 1)) * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT, CHUNK, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gla_recurrent_kernel<T, RPT, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   int threads = (vdim * R + 31) / 32 * 32;
   if (threads < dim) threads = (dim + 31) / 32 * 32;                  // thread i < dim owns decay channel i
   if (threads > MAXT) return PHOTON_ERR_UNSUPPORTED;
-  gla_recurrent_kernel<T, RPT, CHUNK, MAXT><<<dim3(S, heads), dim3(threads), smem, stream>>>(
+  gla_recurrent_kernel<T, RPT, MAXT><<<dim3(S, heads), dim3(threads), smem, stream>>>(
       (const T*)q, (const T*)k, (const T*)v, (const T*)g, (const T*)low, in_stride, rank, (const T*)w_a2, b_a2, b_bf16,
       norm_w, norm_w_bf16, eps, inv_tau,
-      qscale, cu_tokens, state_slots, state, num_slots, (T*)out, out_stride, heads, dim, vdim, err, first, count, chunk,
-      o_loc, b_out, s_loc, skip_from);
+      qscale, cu_tokens, state_slots, state, num_slots, (T*)out, out_stride, heads, dim, vdim, err, skip_from);
   return launch_status();
 }
 
@@ -474,22 +446,20 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
   gla_shape(dim, vdim, &rpt, &maxt);
 #define GLA_ARGS q, k, v, g, low, in_stride, rank, w_a2, b_a2, bb, norm_w, wb, eps, it, qscale, cu_tokens, state_slots, state, \
                  num_slots, out, out_stride, S, heads, dim, vdim, err, stream
-#define GLA_DISPATCH_T(CHUNK, MAXT, ...)                                                 \
-  if (dtype == PHOTON_BF16) {                                                            \
-    if (rpt == 8) return gla_launch<bf16, 8, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);        \
-    if (rpt == 16) return gla_launch<bf16, 16, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);      \
-    if (rpt == 32) return gla_launch<bf16, 32, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);      \
-    return gla_launch<bf16, 64, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);                     \
-  }                                                                                      \
-  if (rpt == 8) return gla_launch<float, 8, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);         \
-  if (rpt == 16) return gla_launch<float, 16, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);       \
-  if (rpt == 32) return gla_launch<float, 32, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);       \
-  return gla_launch<float, 64, CHUNK, MAXT>(GLA_ARGS, __VA_ARGS__);
-#define GLA_DISPATCH(CHUNK, ...)                                                         \
-  if (maxt == 1024) { GLA_DISPATCH_T(CHUNK, 1024, __VA_ARGS__) }                         \
-  if (maxt == 512) { GLA_DISPATCH_T(CHUNK, 512, __VA_ARGS__) }                           \
-  GLA_DISPATCH_T(CHUNK, 256, __VA_ARGS__)
-  GLA_DISPATCH(false, 0, 0, 0, nullptr, nullptr, nullptr, skip_from)
+#define GLA_DISPATCH_T(MAXT)                                                      \
+  if (dtype == PHOTON_BF16) {                                                     \
+    if (rpt == 8) return gla_launch<bf16, 8, MAXT>(GLA_ARGS, skip_from);          \
+    if (rpt == 16) return gla_launch<bf16, 16, MAXT>(GLA_ARGS, skip_from);        \
+    if (rpt == 32) return gla_launch<bf16, 32, MAXT>(GLA_ARGS, skip_from);        \
+    return gla_launch<bf16, 64, MAXT>(GLA_ARGS, skip_from);                       \
+  }                                                                               \
+  if (rpt == 8) return gla_launch<float, 8, MAXT>(GLA_ARGS, skip_from);           \
+  if (rpt == 16) return gla_launch<float, 16, MAXT>(GLA_ARGS, skip_from);         \
+  if (rpt == 32) return gla_launch<float, 32, MAXT>(GLA_ARGS, skip_from);         \
+  return gla_launch<float, 64, MAXT>(GLA_ARGS, skip_from);
+  if (maxt == 1024) { GLA_DISPATCH_T(1024) }
+  if (maxt == 512) { GLA_DISPATCH_T(512) }
+  GLA_DISPATCH_T(256)
 }
 
 // One long prompt portion (tokens first .. first + count - 1 of the step, state slot `slot`) in chunks that run side by
