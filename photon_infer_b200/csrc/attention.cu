@@ -58,9 +58,20 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
   const int kstart = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int* table = block_table + (size_t)seq * max_pages;
 
-  for (int i = tid; i < G * d; i += ATT_THREADS) {
-    const int h = i / d, j = i - h * d;
-    qs[i] = to_f32(q[(size_t)t * q_stride + (size_t)(h0 + h) * d + j]);
+  {
+    // the block's query heads lie side by side in the row: 16 bytes per load where the row allows it
+    constexpr int QV = 16 / sizeof(T);
+    const T* qrow = q + (size_t)t * q_stride + (size_t)h0 * d;
+    if ((G * d) % QV == 0 && (uintptr_t)qrow % 16 == 0) {
+      for (int i = tid * QV; i < G * d; i += ATT_THREADS * QV) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(qrow + i);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int u = 0; u < QV; ++u) qs[i + u] = to_f32(e[u]);
+      }
+    } else {
+      for (int i = tid; i < G * d; i += ATT_THREADS) qs[i] = to_f32(qrow[i]);
+    }
   }
   for (int h = tid; h < G; h += ATT_THREADS) { mrun[h] = -INFINITY; lsum[h] = 0.f; corr[h] = 0.f; }
   float acc[PPT];

@@ -18,7 +18,9 @@ class SwiGLUFeedForward(FeedForward):
     kernel_modules = ("elementwise",)
 
     def required_kernels(self, dtype):
-        return ["elementwise"] + (["gemm_skinny", "gemm_skinny_fused", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
+        if dtype != torch.bfloat16:
+            return ["elementwise"]
+        return ["elementwise", "gemm_skinny", "gemm_tc", "gemm_tc2"] + (["gemm_skinny_fused"] if self.fuse_norm else [])
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):

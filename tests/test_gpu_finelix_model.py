@@ -9,7 +9,10 @@ expert than the 64-bit oracle where two router logits lie closer than the roundi
 position is far off and says nothing about the kernels, so the bfloat16 comparison with the oracle allows 3 % of
 the positions to exceed the bound.  How a request is cut must not matter in either dtype.
 """
+import os
 import random
+import subprocess
+import sys
 
 import numpy as np
 import pytest
@@ -183,3 +186,20 @@ def test_greedy_generation_through_the_engine(tmp_path, name, lengths, slots):
     plain = PlainFinelix.from_folder(folder)
     for rid, p in zip(rids, prompts):
         assert list(out[rid]) == plain.greedy(p, 10)
+
+
+def test_command_line(tmp_path):
+    """``bin/llama_infer`` picks the model class by config.json: the same command line serves a Finelix folder."""
+    from plain.finelix_plain import PlainFinelix
+    folder = make_finelix_folder(str(tmp_path / "m"), "fx_d")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompt = random_ids(11, TINY_FINELIX["fx_d"]["config"]["vocab"], seed=5)
+    cmd = [sys.executable, os.path.join(root, "bin", "llama_infer"), folder, "cuda", "--dtype", "fp32", "--prompt-ids",
+           ",".join(map(str, prompt)), "--prompt-ids", "7 8 9", "--max-new-tokens", "6", "--temperature", "0", "--ignore-eos",
+           "--num-blocks", "32", "--max-sequences", "4", "--max-model-len", "128"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    lines = [l for l in res.stdout.splitlines() if l.startswith("request")]
+    m = PlainFinelix.from_folder(folder)
+    assert lines[0].split(": ")[1].split() == [str(t) for t in m.greedy(prompt, 6)]
+    assert lines[1].split(": ")[1].split() == [str(t) for t in m.greedy([7, 8, 9], 6)]

@@ -97,18 +97,20 @@ def test_loop_input(dtype):
         part.forward(x.to(DEV), None, x0.to(DEV), 3, None)
 
 
-def _latent_part(dtype, heads=3, dim=16, rot=8, vdim=20, kv_rank=32, q_rank=24, H=48, base=10000.0, seed=5):
+def _latent_part(dtype, heads=3, dim=16, rot=8, vdim=20, kv_rank=32, q_rank=24, H=48, base=10000.0, seed=5, rot_dims=None):
     from photon_infer_b200.parts.registry import create_part
+    rot_dims = rot if rot_dims is None else rot_dims
     m = dict(heads=heads, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=(dim + rot) ** -0.5,
-             rot=dict(base=base, dims=rot))
+             rot=dict(base=base, dims=rot_dims))
     att = create_part("mixer", "latent_attention", dict(hidden_size=H, heads=heads, dim=dim, rot_dim=rot, vdim=vdim,
                                                         kv_rank=kv_rank, q_rank=q_rank, scale=m["scale"], eps=1e-5,
-                                                        rot_base=base, rot_dims=rot))
+                                                        rot_base=base, rot_dims=rot_dims))
     return att, m, _weights(att, dtype, 0.3, seed)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [dict(), dict(heads=1, dim=24, rot=16, vdim=8, kv_rank=40, q_rank=8, base=1e6)])
+@pytest.mark.parametrize("shape", [dict(), dict(heads=1, dim=24, rot=16, vdim=8, kv_rank=40, q_rank=8, base=1e6),
+                                   dict(heads=2, dim=8, rot=16, vdim=8, kv_rank=24, q_rank=16, rot_dims=8)])   # part of the rotated features turns
 @pytest.mark.parametrize("long", [False, True])
 def test_latent_attention_two_requests_in_portions(dtype, shape, long):
     """The mixer alone: two requests, each fed in three steps (a long portion, two tokens, single tokens), against
