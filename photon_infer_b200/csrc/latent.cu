@@ -331,3 +331,172 @@ PHOTON_API int photon_causal_softmax_rows(const float* scores, long ld, void* pr
     causal_softmax_kernel<float><<<rows, 256, 0, stream>>>(scores, ld, (float*)probs, ldp, heads, first_pos, cols, scale);
   return launch_status();
 }
+
+// ---------------------------------------------------------------- decoded tokens on the tensor cores
+// All heads of a token attend to the same cached rows, so a decoded token is a (heads x width) by (width x keys)
+// product followed by a (heads x keys) by (keys x kv_rank) one.  Block (t, s) takes token t and the 64 keys
+// s * 64 .. of its request: the rows come into shared memory once (16-byte loads through the block table) and
+// serve every tile of 16 heads; scores = Q C^T with wmma (bfloat16 in, 32-bit accumulate), a softmax over the
+// block's keys in 32-bit, P (rounded to bfloat16) times the first kv_rank columns of the same rows.  Every block
+// leaves its unnormalised sums with the rows' maximum and denominator, in the layout of the general kernel's
+// shares, and a second kernel puts the shares of a (token, head) together in their order.
+#include <mma.h>
+using namespace nvcuda;
+
+#define LD_KEYS 64
+
+__global__ void __launch_bounds__(128)
+latent_decode_kernel(const bf16* __restrict__ q, long q_stride, const bf16* __restrict__ cache,
+                     const int* __restrict__ block_table, int max_pages, const int* __restrict__ token_seq,
+                     const int* __restrict__ positions, int heads, int width, int dv, int page_size, int num_pages,
+                     float scale, int splits, float* __restrict__ part, int* err) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int t = blockIdx.x, s = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ldk = width + 8;                                   // bfloat16 elements; rows of 16 keys stay 32-byte aligned
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                // 64 x ldk
+  bf16* Qs = Ks + LD_KEYS * ldk;                               // 16 x ldk
+  float* Sf = reinterpret_cast<float*>(Qs + 16 * ldk);         // 16 x 68
+  bf16* Ps = reinterpret_cast<bf16*>(Sf + 16 * 68);            // 16 x 72
+  float* Ot = reinterpret_cast<float*>(Ps + 16 * 72);          // 4 x 16 x 20
+  float* rowm = Ot + 4 * 16 * 20;                              // 16
+  float* rowl = rowm + 16;                                     // 16
+  const int p = positions[t];
+  const int k0 = s * LD_KEYS;
+  const int nkeys = min(LD_KEYS, p + 1 - k0);                  // keys of this block that the token sees
+  if (nkeys <= 0) {                                            // an empty share: the merge skips it
+    for (int h = tid; h < heads; h += 128) {
+      float* dst = part + (((size_t)t * heads + h) * splits + s) * (dv + 2);
+      dst[dv] = -INFINITY; dst[dv + 1] = 0.f;
+    }
+    return;
+  }
+  const int* table = block_table + (size_t)token_seq[t] * max_pages;
+  const int vecs = width / 8;
+  for (int i = tid; i < LD_KEYS * vecs; i += 128) {
+    const int key = i / vecs, j = (i - key * vecs) * 8;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (key < nkeys) {
+      const int kk = k0 + key;
+      const int page = table[kk / page_size];
+      if (page < 0 || page >= num_pages) report_error(err, PHOTON_DEV_BAD_PAGE, t, kk, page);
+      else raw = *reinterpret_cast<const uint4*>(cache + ((size_t)page * page_size + kk % page_size) * width + j);
+    }
+    *reinterpret_cast<uint4*>(Ks + key * ldk + j) = raw;
+  }
+  for (int h0 = 0; h0 < heads; h0 += 16) {
+    __syncthreads();                                           // the rows are in; the last tile of heads is done with Qs
+    for (int i = tid; i < 16 * vecs; i += 128) {
+      const int h = i / vecs, j = (i - h * vecs) * 8;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (h0 + h < heads) raw = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)(h0 + h) * width + j);
+      *reinterpret_cast<uint4*>(Qs + h * ldk + j) = raw;
+    }
+    __syncthreads();
+    {   // scores of 16 heads x 16 keys per warp
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
+      for (int k = 0; k < width; k += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
+        wmma::load_matrix_sync(a, Qs + k, ldk);
+        wmma::load_matrix_sync(b, Ks + (size_t)warp * 16 * ldk + k, ldk);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      wmma::store_matrix_sync(Sf + warp * 16, acc, 68, wmma::mem_row_major);
+    }
+    __syncthreads();
+    {   // softmax over the block's keys: eight lanes a row, eight keys a lane
+      const int row = tid >> 3, c0 = (tid & 7) * 8;
+      float v[8], m = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        v[u] = c0 + u < nkeys ? Sf[row * 68 + c0 + u] * scale : -INFINITY;
+        m = fmaxf(m, v[u]);
+      }
+      for (int d = 1; d < 8; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+      float l = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float e = v[u] == -INFINITY ? 0.f : expf(v[u] - m);
+        l += e;
+        Ps[row * 72 + c0 + u] = __float2bfloat16_rn(e);
+      }
+      for (int d = 1; d < 8; d <<= 1) l += __shfl_xor_sync(0xffffffffu, l, d);
+      if ((tid & 7) == 0) { rowm[row] = m; rowl[row] = l; }
+    }
+    __syncthreads();
+    for (int nt = warp; nt < dv / 16; nt += 4) {               // 16 heads x 16 value columns per tile
+      wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+      wmma::fill_fragment(acc, 0.f);
+#pragma unroll
+      for (int kk = 0; kk < LD_KEYS; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+        wmma::load_matrix_sync(a, Ps + kk, 72);
+        wmma::load_matrix_sync(b, Ks + (size_t)kk * ldk + nt * 16, ldk);
+        wmma::mma_sync(acc, a, b, acc);
+      }
+      float* stage = Ot + warp * 16 * 20;
+      wmma::store_matrix_sync(stage, acc, 20, wmma::mem_row_major);
+      __syncwarp();
+      for (int e = lane; e < 256; e += 32) {
+        const int h = e >> 4, c = e & 15;
+        if (h0 + h < heads)
+          part[(((size_t)t * heads + h0 + h) * splits + s) * (dv + 2) + nt * 16 + c] = stage[h * 20 + c];
+      }
+      __syncwarp();
+    }
+    if (tid < 16 && h0 + tid < heads) {
+      float* dst = part + (((size_t)t * heads + h0 + tid) * splits + s) * (dv + 2);
+      dst[dv] = rowm[tid]; dst[dv + 1] = rowl[tid];
+    }
+  }
+}
+
+__global__ void latent_merge_kernel(const float* __restrict__ part, int splits, int dv, bf16* __restrict__ out,
+                                    long out_stride, int heads) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* src = part + ((size_t)t * heads + h) * splits * (dv + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[s * (dv + 2) + dv]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = src[s * (dv + 2) + dv];
+    if (ms != -INFINITY) l += src[s * (dv + 2) + dv + 1] * expf(ms - m);
+  }
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = src[s * (dv + 2) + dv];
+      if (ms != -INFINITY) a += src[s * (dv + 2) + j] * expf(ms - m);
+    }
+    out[(size_t)t * out_stride + (size_t)h * dv + j] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+  }
+}
+
+// q [T][heads * width] bfloat16 (row stride in elements), cache [num_pages * page_size][width] bfloat16, out
+// [T][heads * dv]: token t at position positions[t] of request token_seq[t] sees the rows 0 .. positions[t]; a row's
+// value is its first dv numbers.  width and dv multiples of 16.  splits >= ceil((largest position + 1) / 64);
+// part: float [T * heads * splits * (dv + 2)].
+PHOTON_API int photon_latent_decode_attention(const void* q, long q_stride, const void* cache, const int* block_table,
+                                              int max_pages, const int* token_seq, const int* positions, int T_,
+                                              int heads, int width, int dv, int page_size, int num_pages, float scale,
+                                              int splits, float* part, void* out, long out_stride, int* err,
+                                              cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (heads <= 0 || splits <= 0 || part == nullptr || dv > width) return PHOTON_ERR_ARGUMENT;
+  if (width % 16 || dv % 16 || q_stride % 8 || (uintptr_t)q % 16 || (uintptr_t)cache % 16 || splits > 65535 || heads > 65535)
+    return PHOTON_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(LD_KEYS + 16) * (width + 8) * 2 + 16 * 68 * 4 + 16 * 72 * 2 + 4 * 16 * 20 * 4 + 32 * 4;
+  if (smem > 220 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  latent_decode_kernel<<<dim3(T_, splits), 128, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, block_table,
+      max_pages, token_seq, positions, heads, width, dv, page_size, num_pages, scale, splits, part, err);
+  int st = launch_status();
+  if (st != 0) return st;
+  latent_merge_kernel<<<dim3(T_, heads), 128, 0, stream>>>(part, splits, dv, (bf16*)out, out_stride, heads);
+  return launch_status();
+}

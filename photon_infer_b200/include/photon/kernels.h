@@ -118,6 +118,14 @@ PHOTON_EXPORT int photon_gather_rows(const void* cache, int dtype, const int* ta
 PHOTON_EXPORT int photon_causal_softmax_rows(const float* scores, long ld, void* probs, long ldp, int dtype, int rows, int heads,
                                int first_pos, int cols, float scale, cudaStream_t stream);
 
+/* Decoded tokens on the tensor cores (bfloat16; width and dv multiples of 16): token t sees the rows 0 .. positions[t] of
+ * request token_seq[t]; a row's value is its first dv numbers.  splits >= ceil((largest position + 1) / 64); part: float
+ * [T * heads * splits * (dv + 2)]. */
+PHOTON_EXPORT int photon_latent_decode_attention(const void* q, long q_stride, const void* cache, const int* block_table,
+                                   int max_pages, const int* token_seq, const int* positions, int T_, int heads, int width,
+                                   int dv, int page_size, int num_pages, float scale, int splits, float* part, void* out,
+                                   long out_stride, int* err, cudaStream_t stream);
+
 /* ------------------------------------------------------------------ gla.cu: gated linear attention (recurrent state) */
 /* Per (request, head): S = diag(a_t) S + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau), z_t = w_a2 low_t + b_a2, o_t = S^T (q_t *
  * qscale); out = o_t / rms(o_t) * norm_w * silu(g_t).  q, k [T][heads * dim], v, g [T][heads * vdim] and low [T][rank] share

@@ -857,6 +857,39 @@ def latent_q_rope(q: torch.Tensor, heads: int, dim: int, rot: int, rot_dims: int
              out.stride(0), out.shape[2], out_off, T, _stream()), "latent_q_rope")
 
 
+def latent_decode_supported(q: torch.Tensor, width: int, value_dim: int) -> bool:
+    """The tensor-core kernel for decoded tokens over a cached latent: bfloat16, row and value widths multiples of 16."""
+    return (q.dtype == torch.bfloat16 and width % 16 == 0 and value_dim % 16 == 0 and value_dim <= width
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and (80 * (width + 8) * 2 + 16384) <= 220 * 1024)
+
+
+def latent_decode_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                            token_seq: torch.Tensor, positions: torch.Tensor, heads: int, width: int, value_dim: int,
+                            scale: float, max_context: int, err: Optional[torch.Tensor]) -> None:
+    """Attention of decoded tokens (or of the few tokens of a short portion) over cached latent rows on the tensor
+    cores: ``q [T, heads * width]``, ``cache [pages, 1, page_size, width]``, ``out [T, heads * value_dim]``; every token
+    sees the rows up to its own position, a row's value is its first ``value_dim`` numbers.  ``max_context``: an upper
+    bound of the tokens' contexts (sizes the grid: one block per token and 64 rows)."""
+    _cuda(q, out, cache, block_table, token_seq, positions, err)
+    T = q.shape[0]
+    if not latent_decode_supported(q, width, value_dim) or q.shape[1] != heads * width or q.stride(1) != 1 \
+            or out.shape != (T, heads * value_dim) or out.stride(1) != 1 or out.dtype != q.dtype or cache.dtype != q.dtype \
+            or cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != width or not cache.is_contiguous():
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "latent_decode_attention: bfloat16, widths that are multiples of 16")
+    for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
+        _int32(t, name)
+    splits = max(1, -(-int(max_context) // 64))
+    part = torch.empty(T * heads * splits * (value_dim + 2), dtype=torch.float32, device=q.device)
+    f = _fn("latent", "photon_latent_decode_attention",
+            [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_float, c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T,
+             heads, width, value_dim, cache.shape[2], cache.shape[0], float(scale), splits, _ptr(part), _ptr(out),
+             out.stride(0), _ptr(err), _stream()), "latent_decode_attention")
+    global _launch_count
+    _launch_count += 1
+
+
 #: From this many rows on the bfloat16 per-head products go to the library's batched product.
 HEAD_LINEAR_LIBRARY_ROWS = 16
 

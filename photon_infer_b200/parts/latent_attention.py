@@ -126,6 +126,14 @@ class LatentAttention(Mixer):
     def _paged(self, q_lat, o_lat, ctx, cache, a: int, b: int) -> None:
         n = self.heads
         group = ctx.groups[cache.group]
+        q2 = q_lat[a:b].view(b - a, n * self.width)
+        shares = -(-max(ctx.max_context_len, 1) // 64)
+        if self.window is None and ops.latent_decode_supported(q2, self.width, self.kv_rank) \
+                and (b - a) * n * shares * (self.kv_rank + 2) * 4 <= DECODE_SHARES_BYTES:
+            # bfloat16 with widths that fit the tensor cores' tiles: one block per token and 64 cached rows
+            ops.latent_decode_attention(q2, o_lat[a:b], cache.k, group.block_table, ctx.token_seq[a:b], ctx.positions[a:b], n,
+                                        self.width, self.kv_rank, self.scale, ctx.max_context_len, ctx.error_flag)
+            return
         splits = 1
         if q_lat.dtype == torch.bfloat16:
             # few tokens with long contexts: share every token's key tiles out until the GPU is full (the float32 run keeps
@@ -150,6 +158,9 @@ class LatentAttention(Mixer):
             torch.mm(probs, rows[:keys, :kr], out=o[t0:t1].view((t1 - t0) * n, kr))
 
 
+#: The tensor-core decode kernel leaves one share per token, head and 64 rows of the longest context the step allows;
+#: beyond this many bytes of shares the step takes the general kernel, which bounds its shares by the GPU's size.
+DECODE_SHARES_BYTES = 512 << 20
 #: A request that brings at least this many tokens to a bfloat16 step takes the products-and-softmax path.
 LIBRARY_MIN_TOKENS = 32
 #: Bytes of 32-bit scores held at a time on that path (the queries are cut into slabs that fit).

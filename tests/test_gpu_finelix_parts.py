@@ -110,7 +110,8 @@ def _latent_part(dtype, heads=3, dim=16, rot=8, vdim=20, kv_rank=32, q_rank=24, 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [dict(), dict(heads=1, dim=24, rot=16, vdim=8, kv_rank=40, q_rank=8, base=1e6),
-                                   dict(heads=2, dim=8, rot=16, vdim=8, kv_rank=24, q_rank=16, rot_dims=8)])   # part of the rotated features turns
+                                   dict(heads=2, dim=8, rot=16, vdim=8, kv_rank=24, q_rank=16, rot_dims=8),   # part of the rotated features turns
+                                   dict(heads=3, dim=16, rot=16, vdim=20, kv_rank=32, q_rank=24)])            # widths of 16s: tensor-core decode
 @pytest.mark.parametrize("long", [False, True])
 def test_latent_attention_two_requests_in_portions(dtype, shape, long):
     """The mixer alone: two requests, each fed in three steps (a long portion, two tokens, single tokens), against
@@ -183,6 +184,40 @@ def test_latent_rows_far_back_at_page_borders_and_at_the_start(dtype, target):
                             None, 1.0, None, value_dim=dv)
         want2 = torch.softmax(scores[:, :n - 1], dim=1) @ rows.to(dtype).double()[:n - 1, :dv]
         assert rel_err(out.float().cpu().view(heads, dv), want2) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("heads", [5, 16, 20])
+@pytest.mark.parametrize("target", [0, 1, 63, 64, 65, 127, 128, 300, 598, 599])
+def test_latent_rows_on_the_tensor_cores(heads, target):
+    """The same made-to-stand-out row for the tensor-core kernel of decoded tokens (one block per token and 64 rows): the
+    borders of its blocks of 64 rows, the first rows and the last, with heads that fill part of a tile, one tile, and
+    more; two tokens of different requests and lengths in one call."""
+    from photon_infer_b200.kernels import ops
+    width, dv, ps, n = 48, 32, 16, 600
+    g = torch.Generator().manual_seed(1000 + target)
+    rows = torch.randn(n, width, generator=g)
+    rows = rows / rows.norm(dim=1, keepdim=True)
+    q = torch.randn(heads, width, generator=g)
+    rows[target] = q.mean(0) / q.mean(0).norm()
+    qs = 14.0 * rows[target].expand(heads, width).clone() + 0.1 * q / q.norm(dim=1, keepdim=True)
+    pages = (n + ps - 1) // ps
+    perm = torch.randperm(pages, generator=g)
+    cache = torch.zeros(pages, 1, ps, width)
+    for p in range(n):
+        cache[perm[p // ps], 0, p % ps] = rows[p]
+    cache = cache.bfloat16().to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    bt = i32([perm.tolist(), perm.tolist()])
+    rb, qb = rows.bfloat16().double(), qs.bfloat16().double()
+    short = max(target + 1, 70)                                            # the second token's request is shorter
+    qq = torch.stack([qs.reshape(-1), qs.reshape(-1)]).bfloat16().to(DEV)
+    out = torch.empty(2, heads * dv, dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.latent_decode_attention(qq, out, cache, bt, i32([0, 1]), i32([n - 1, short - 1]), heads, width, dv, 1.0, n, err)
+    assert err.cpu().tolist()[0] == 0
+    for row, length in ((0, n), (1, short)):
+        want = torch.softmax(qb @ rb[:length].T, dim=1) @ rb[:length, :dv]
+        assert rel_err(out[row].float().cpu().view(heads, dv), want) < 1.5e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
