@@ -337,8 +337,9 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int t0 = first + c * chunk, n = min(first + count, t0 + chunk) - t0;
   float* Ss = sm;                         // dim x vdim
-  float* qb = Ss + ((dim * vdim + 3) & ~3);   // dim x chunk, 16-byte aligned
-  float* os = qb + chunk * dim;           // chunk x vdim
+  const int qld = chunk + 4;                  // a channel's stride in qb: neighbouring channels start four banks apart
+  float* qb = Ss + ((dim * vdim + 3) & ~3);   // dim x qld, 16-byte aligned
+  float* os = qb + qld * dim;             // chunk x vdim
   const float* src = s_start + ((size_t)c * heads + h) * dim * vdim;
   if ((dim * vdim) % 4 == 0) {
     for (int e = tid; e < dim * vdim / 4; e += 256) reinterpret_cast<float4*>(Ss)[e] = reinterpret_cast<const float4*>(src)[e];
@@ -348,7 +349,7 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
   // the decayed queries, transposed: qb[i][t], so that eight tokens of one channel are two 16-byte reads
   for (int e = tid; e < chunk * dim; e += 256) {
     const int t = e / dim, i = e - t * dim;
-    qb[i * chunk + t] = t < n ? to_f32(q[(size_t)(t0 + t) * in_stride + (size_t)h * dim + i]) * qscale *
+    qb[i * qld + t] = t < n ? to_f32(q[(size_t)(t0 + t) * in_stride + (size_t)h * dim + i]) * qscale *
                                     b[((size_t)(t0 + t) * heads + h) * dim + i] : 0.f;
   }
   __syncthreads();
@@ -371,8 +372,8 @@ gla_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ g, long in_s
 #pragma unroll
         for (int w = 0; w < 4; ++w) sv[w] = j + w < vdim ? Ss[i * vdim + j + w] : 0.f;
       }
-      const float4 q0 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8);
-      const float4 q1 = *reinterpret_cast<const float4*>(qb + i * chunk + tg * 8 + 4);
+      const float4 q0 = *reinterpret_cast<const float4*>(qb + i * qld + tg * 8);
+      const float4 q1 = *reinterpret_cast<const float4*>(qb + i * qld + tg * 8 + 4);
       const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
       for (int u = 0; u < 8; ++u)
@@ -476,7 +477,7 @@ PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, c
     return PHOTON_ERR_ARGUMENT;
   if (heads > 65535) return PHOTON_ERR_UNSUPPORTED;
   const int chunks = (count + chunk - 1) / chunk;
-  const size_t smem_out = ((size_t)dim * vdim + 4 + (size_t)chunk * (dim + vdim)) * sizeof(float);
+  const size_t smem_out = ((size_t)dim * vdim + 4 + (size_t)(chunk + 4) * dim + (size_t)chunk * vdim) * sizeof(float);
   if (smem_out > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   // the scratch is indexed by the token's place in the step: its three parts are laid out for tokens first ..
   float* o_loc = scratch - (size_t)first * heads * vdim;

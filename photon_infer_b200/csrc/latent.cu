@@ -372,15 +372,25 @@ latent_decode_kernel(const bf16* __restrict__ q, long q_stride, const bf16* __re
   }
   const int* table = block_table + (size_t)token_seq[t] * max_pages;
   const int vecs = width / 8;
-  for (int i = tid; i < LD_KEYS * vecs; i += 128) {
-    const int key = i / vecs, j = (i - key * vecs) * 8;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (key < nkeys) {
-      const int kk = k0 + key;
+  // where each of the block's rows lies, looked up once; the loads of the rows then depend on nothing but this list
+  long long* rowbase = reinterpret_cast<long long*>(rowl + 16);
+  if (tid < LD_KEYS) {
+    long long base = -1;
+    if (tid < nkeys) {
+      const int kk = k0 + tid;
       const int page = table[kk / page_size];
       if (page < 0 || page >= num_pages) report_error(err, PHOTON_DEV_BAD_PAGE, t, kk, page);
-      else raw = *reinterpret_cast<const uint4*>(cache + ((size_t)page * page_size + kk % page_size) * width + j);
+      else base = ((long long)page * page_size + kk % page_size) * width;
     }
+    rowbase[tid] = base;
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int i = tid; i < LD_KEYS * vecs; i += 128) {
+    const int key = i / vecs, j = (i - key * vecs) * 8;
+    const long long base = rowbase[key];
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (base >= 0) raw = *reinterpret_cast<const uint4*>(cache + base + j);
     *reinterpret_cast<uint4*>(Ks + key * ldk + j) = raw;
   }
   for (int h0 = 0; h0 < heads; h0 += 16) {
@@ -487,7 +497,7 @@ PHOTON_API int photon_latent_decode_attention(const void* q, long q_stride, cons
   if (heads <= 0 || splits <= 0 || part == nullptr || dv > width) return PHOTON_ERR_ARGUMENT;
   if (width % 16 || dv % 16 || q_stride % 8 || (uintptr_t)q % 16 || (uintptr_t)cache % 16 || splits > 65535 || heads > 65535)
     return PHOTON_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)(LD_KEYS + 16) * (width + 8) * 2 + 16 * 68 * 4 + 16 * 72 * 2 + 4 * 16 * 20 * 4 + 32 * 4;
+  const size_t smem = (size_t)(LD_KEYS + 16) * (width + 8) * 2 + 16 * 68 * 4 + 16 * 72 * 2 + 4 * 16 * 20 * 4 + 32 * 4 + LD_KEYS * 8;
   if (smem > 220 * 1024) return PHOTON_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(latent_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -991,7 +991,7 @@ def gla_chunked_supported(dim: int, vdim: int, rank: int = 64) -> bool:
             p *= 2
         if p <= 32 and vdim * p <= 512 and dim <= 512:
             local = (3 * GLA_CHUNK * groups * (rpt + 4) + GLA_CHUNK * vdim + dim * (rank + 2)) * 4
-            out = (dim * vdim + 4 + GLA_CHUNK * (dim + vdim)) * 4
+            out = (dim * vdim + 4 + (GLA_CHUNK + 4) * dim + GLA_CHUNK * vdim) * 4
             return local <= 220 * 1024 and out <= 200 * 1024
     return False
 
