@@ -465,8 +465,8 @@ PHOTON_API int photon_gla_recurrent(const void* q, const void* k, const void* v,
 
 // One long prompt portion (tokens first .. first + count - 1 of the step, state slot `slot`) in chunks that run side by
 // side: every chunk's own recurrence from zero, a scan over the chunks' end states, and the start states' share of the
-// outputs with the norm and the gate.  scratch: float [count * heads * (vdim + dim) + chunks * heads * dim * vdim] with
-// chunks = ceil(count / chunk).  The sums differ from the token-by-token kernel's in their order only.
+// outputs with the norm and the gate.  scratch: float [count * heads * (vdim + dim) + 4 + chunks * heads * dim * vdim]
+// with chunks = ceil(count / chunk), 16-byte aligned.  The sums differ from the token-by-token kernel's in their order only.
 PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, const void* g, const void* low,
                                   long in_stride, int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype,
                                   const void* norm_w, int norm_w_dtype, float eps, float tau, float qscale, int first,
@@ -482,7 +482,7 @@ PHOTON_API int photon_gla_chunked(const void* q, const void* k, const void* v, c
   // the scratch is indexed by the token's place in the step: its three parts are laid out for tokens first ..
   float* o_loc = scratch - (size_t)first * heads * vdim;
   float* b = scratch + (size_t)count * heads * vdim - (size_t)first * heads * dim;
-  float* s_loc = scratch + (size_t)count * heads * (vdim + dim);
+  float* s_loc = scratch + (((size_t)count * heads * (vdim + dim) + 3) & ~(size_t)3);   // 16-byte aligned: read four at a time
   const int wb = norm_w_dtype == PHOTON_BF16, bb = b_a2_dtype == PHOTON_BF16;
   const float it = 1.0f / tau;
   int rp = 1;

@@ -137,8 +137,8 @@ PHOTON_EXPORT int photon_gla_recurrent(const void* q, const void* k, const void*
                          float* state, int num_slots, void* out, long out_stride, int S, int heads, int dim, int vdim,
                          int skip_from, int* err, cudaStream_t stream);
 /* One long prompt portion (tokens first .. first + count - 1 of the step, state slot `slot`, negative: from zero, nothing
- * stored) in chunks of `chunk` tokens that run side by side.  scratch: float [count * heads * (vdim + dim) +
- * ceil(count / chunk) * heads * dim * vdim].  photon_gla_recurrent leaves requests of skip_from tokens or more
+ * stored) in chunks of `chunk` tokens that run side by side.  scratch: float [count * heads * (vdim + dim) + 4 +
+ * ceil(count / chunk) * heads * dim * vdim], 16-byte aligned.  photon_gla_recurrent leaves requests of skip_from tokens or more
  * (skip_from > 0) to this path. */
 PHOTON_EXPORT int photon_gla_chunked(const void* q, const void* k, const void* v, const void* g, const void* low, long in_stride,
                        int dtype, int rank, const void* w_a2, const void* b_a2, int b_a2_dtype, const void* norm_w,

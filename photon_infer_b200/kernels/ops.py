@@ -1007,7 +1007,7 @@ def gla_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tens
     _cuda(q, k, v, g, low, w_a2, b_a2, norm_w, state, out, err)
     rank = low.shape[1]
     chunks = -(-count // GLA_CHUNK)
-    scratch = torch.empty(count * heads * (vdim + dim) + chunks * heads * dim * vdim, dtype=torch.float32, device=q.device)
+    scratch = torch.empty(count * heads * (vdim + dim) + 4 + chunks * heads * dim * vdim, dtype=torch.float32, device=q.device)
     f = _fn("gla", "photon_gla_chunked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
              c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long,

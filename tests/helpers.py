@@ -181,6 +181,14 @@ TINY_FINELIX: Dict[str, dict] = {
                             dict(type="latent_attention", mixer=_latent(2, 12, 4, 8, 20, 12), mlp=dict(kind="dense", ff=40))],
                     loop=dict(start=1, stop=2, times=1)),
         seed=14, init_std=0.15, norm_std=0.1, block_size=16),
+    # sizes that are multiples of nothing: no 16-byte rows anywhere, so every kernel takes its unaligned path
+    "fx_e": dict(
+        config=dict(architecture="Finelix", vocab=77, width=50, embedding=dict(scale=3.0), norm=dict(eps=1e-5),
+                    layers=[dict(type="latent_attention", mixer=_latent(3, 10, 6, 14, 36, 26), mlp=dict(kind="dense", ff=70)),
+                            dict(type="gla", mixer=dict(heads=1, dim=9, vdim=33, tau=5.0, decay_rank=3), mlp=None),
+                            dict(type="gla_2", mixer=dict(heads=3, dim=18, vdim=14, tau=3.0), mlp=_moe(6, 2, 30, 22))],
+                    loop=dict(start=0, stop=2, times=2)),
+        seed=15, init_std=0.1, norm_std=0.1, block_size=16),
 }
 
 
