@@ -1,8 +1,8 @@
 """Whole Finelix models through ``bin/trace_run`` and through the engine, against the plain implementation:
 each request whole; a prompt and then its tail token by token; portions of changing size down to two tokens;
 up to four live requests in mixed batches with so few pages and slots that they are used again; long decoding;
-greedy generation through the engine's own entry point and scheduler.  Four tiny configurations that differ in
-every size, in float32 and in bfloat16.
+greedy generation through the engine's own entry point and scheduler.  Five tiny configurations that differ in
+every size (one of them with sizes that are multiples of nothing), in float32 and in bfloat16.
 
 float32 must match the plain implementation at every position.  In bfloat16 a routed layer may pick another
 expert than the 64-bit oracle where two router logits lie closer than the rounding of the activations; such a
