@@ -33,13 +33,18 @@ class CacheGroup:
         self.pool = PagePool(num_pages)
         self.tables: Dict[object, List[int]] = {}
         self.kv: Optional[torch.Tensor] = None
+        self.v_only: Optional[torch.Tensor] = None     # values of another width than the keys: a tensor of their own
         if device is not None:
-            self.kv = torch.zeros((len(entries), spec.planes, num_pages, spec.n_kv_heads, page_size, spec.head_dim),
+            planes = 1 if spec.split_planes else spec.planes
+            self.kv = torch.zeros((len(entries), planes, num_pages, spec.n_kv_heads, page_size, spec.head_dim),
                                   dtype=dtype, device=device)
+            if spec.split_planes:
+                self.v_only = torch.zeros((len(entries), num_pages, spec.n_kv_heads, page_size, spec.value_dim),
+                                          dtype=dtype, device=device)
 
     # ------------------------------------------------------------------ sizes
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.entries) * self.spec.planes * self.spec.n_kv_heads * self.spec.head_dim * element_size
+        return len(self.entries) * self.spec.n_kv_heads * self.spec.row_width * element_size
 
     def first_visible(self, length: int) -> int:
         """First key that a token at position ``length`` (the next one) can still see."""
@@ -88,8 +93,9 @@ class CacheGroup:
             return 0
         table = self.tables[rid]
         keep_from = self.first_visible(length) // self.page_size
+        kept_first = -(-self.spec.keep_first // self.page_size)     # pages of the tokens that stay visible for good
         n = 0
-        for i in range(min(keep_from, len(table))):
+        for i in range(kept_first, min(keep_from, len(table))):
             if table[i] != NO_PAGE:
                 self.pool.free(table[i])
                 table[i] = NO_PAGE

@@ -194,7 +194,10 @@ class CacheManager:
                 lc.shared = self.entry_shared[i]
                 if self.groups[g].kv is not None:
                     lc.k = self.groups[g].kv[slot, 0]
-                    lc.v = self.groups[g].kv[slot, 1] if self.groups[g].spec.values else None
+                    if self.groups[g].v_only is not None:
+                        lc.v = self.groups[g].v_only[slot]
+                    else:
+                        lc.v = self.groups[g].kv[slot, 1] if self.groups[g].spec.values else None
             lc.state = self.states.tensors.get(i)
             out.append(lc)
         return out
@@ -212,7 +215,7 @@ class CacheManager:
             for r in rids:
                 n = self._requests[r].length
                 if g.spec.window is not None:
-                    n = min(n, g.spec.window)
+                    n = min(n, g.spec.window + g.spec.keep_first)
                 total += n * g.bytes_per_token(es)
         return total
 

@@ -24,24 +24,7 @@ MIXER_TYPES = ("latent_attention", "gla", "gla_2")
 DEFAULT_MAX_POSITIONS = 131072
 
 
-def _bad(msg: str) -> PhotonError:
-    return PhotonError(ErrorCode.INVALID_CONFIG, "config.json: " + msg)
-
-
-def _num(d: Dict[str, Any], key: str, where: str, kind=int, positive: bool = True, default=None):
-    if not isinstance(d, dict):
-        raise _bad(f"'{where}' must be an object")
-    if key not in d or d[key] is None:
-        if default is not None:
-            return default
-        raise _bad(f"required key '{where}.{key}' is missing")
-    v = d[key]
-    if isinstance(v, bool) or not isinstance(v, (int, float)) or (kind is int and not isinstance(v, int)):
-        raise _bad(f"key '{where}.{key}' must be {'an integer' if kind is int else 'a number'}, got {v!r}")
-    v = kind(v)
-    if positive and not v > 0:
-        raise _bad(f"key '{where}.{key}' must be positive, got {v!r}")
-    return v
+from .nested import bad as _bad, num as _num  # noqa: E402
 
 
 def _check_mixer(kind: str, m: Any, where: str) -> Dict[str, Any]:

@@ -34,7 +34,8 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const int* __restrict__ block_table, int max_pages,
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        int n_q, int n_kv, int d, int dv, int hb, int page_size, int num_pages, int window,
-                       float scale, int splits, float* __restrict__ part, int* err) {
+                       float scale, int splits, float* __restrict__ part, int* err, int keep_first, int sink,
+                       float softcap) {
   extern __shared__ __align__(16) float smem[];
   const int chunks = (n_q / n_kv + hb - 1) / hb;
   const int t = blockIdx.x, g = blockIdx.y / chunks;
@@ -79,20 +80,25 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
   for (int n = 0; n < PPT; ++n) acc[n] = 0.f;
 
   // the key tiles of this block: all of them, or one of `splits` equal shares (blockIdx.z)
-  int tile_lo = kstart / ATT_TILE, tile_hi = p / ATT_TILE + 1;
+  // With a window and kept first keys the walk has two stretches: the tiles of keys 0 .. keep_first - 1 that lie
+  // below the window's first tile, then the window's tiles.  vt counts through both.
+  const int tile_lo = kstart / ATT_TILE, tile_hi = p / ATT_TILE + 1;
+  const int kept_tiles = (keep_first > 0 && kstart > 0) ? min((keep_first + ATT_TILE - 1) / ATT_TILE, tile_lo) : 0;
+  int vt_lo = 0, vt_hi = kept_tiles + tile_hi - tile_lo;
   if (splits > 1) {
-    const int per = (tile_hi - tile_lo + splits - 1) / splits;
-    tile_lo += blockIdx.z * per;
-    tile_hi = min(tile_hi, tile_lo + per);
+    const int per = (vt_hi + splits - 1) / splits;
+    vt_lo = blockIdx.z * per;
+    vt_hi = min(vt_hi, vt_lo + per);
   }
   constexpr int VEC = 16 / sizeof(T);
   const bool vec = (d % VEC == 0) && ((uintptr_t)k_cache % 16 == 0);
-  for (int tile0 = tile_lo * ATT_TILE; tile0 < tile_hi * ATT_TILE; tile0 += ATT_TILE) {
+  for (int vt = vt_lo; vt < vt_hi; ++vt) {
+    const int tile0 = (vt < kept_tiles ? vt : tile_lo + vt - kept_tiles) * ATT_TILE;
     __syncthreads();                          // previous tile fully consumed; qs ready on the first pass
     if (tid < ATT_TILE) {
       const int kk = tile0 + tid;
       long long base = -1;
-      if (kk >= kstart && kk <= p) {
+      if (kk <= p && (kk >= kstart || kk < keep_first)) {
         const int page = table[kk / page_size];
         if (page < 0 || page >= num_pages) {
           report_error(err, PHOTON_DEV_BAD_PAGE, t, kk, page);
@@ -140,6 +146,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
         float dot = 0.f;
         for (int j = 0; j < d; ++j) dot += qh[j] * kr[j];
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
       }
       sc[i] = s;
     }
@@ -178,7 +185,9 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
     const int i = tid + n * ATT_THREADS;
     if (i < G * dv) {
       const int h = i / dv, j = i - h * dv;
-      const float l = lsum[h];
+      float l = lsum[h];
+      // the sink: one more key with score 0 and no value (only the denominator grows)
+      if (sink && splits <= 1) l += expf(-mrun[h]);
       if (splits > 1) {
         // this share's sums as they stand, with the head's running maximum and denominator behind them
         float* dst = part + (((size_t)t * n_q + h0 + h) * splits + blockIdx.z) * (dv + 2);
@@ -194,7 +203,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 // The shares of one (token, head) put together, in the order of the shares.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part, int splits, int dv, T* __restrict__ out,
-                                       long out_stride, int n_q) {
+                                       long out_stride, int n_q, int sink) {
   const int t = blockIdx.x, h = blockIdx.y;
   const float* src = part + ((size_t)t * n_q + h) * splits * (dv + 2);
   float m = -INFINITY;
@@ -204,6 +213,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int split
     const float ms = src[s * (dv + 2) + dv];
     if (ms != -INFINITY) l += src[s * (dv + 2) + dv + 1] * expf(ms - m);
   }
+  if (sink) l += expf(-m);
   for (int j = threadIdx.x; j < dv; j += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < splits; ++s) {
@@ -219,7 +229,7 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
                             const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                             const int* positions, int T_, int n_q, int n_kv, int d, int dv, int hb, int page_size,
                             int num_pages, int window, float scale, int splits, float* part, int* err,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int keep_first, int sink, float softcap) {
   const int G = hb;
   const size_t floats = (size_t)G * d + ATT_TILE * (d + 1) + (v_cache == k_cache ? 0 : ATT_TILE * dv) +
                         (size_t)G * ATT_TILE + 3 * G + 1;
@@ -233,10 +243,11 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
   dim3 grid(T_, n_kv * ((n_q / n_kv + hb - 1) / hb), splits);
   paged_attention_kernel<T, PPT><<<grid, ATT_THREADS, smem, stream>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_table,
-      max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err);
+      max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err,
+      keep_first, sink, softcap);
   int st = launch_status();
   if (st != 0 || splits <= 1) return st;
-  attention_merge_kernel<T><<<dim3(T_, n_q), 128, 0, stream>>>(part, splits, dv, (T*)out, out_stride, n_q);
+  attention_merge_kernel<T><<<dim3(T_, n_q), 128, 0, stream>>>(part, splits, dv, (T*)out, out_stride, n_q, sink);
   return launch_status();
 }
 
@@ -250,7 +261,8 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
   return PHOTON_ERR_UNSUPPORTED;
 
 #define ATT_ARGS q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, token_seq, \
-                 positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err, stream
+                 positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err, stream, \
+                 keep_first, sink, softcap
 
 // window <= 0: all keys.  Strides in elements.  The key cache holds [num_pages][n_kv][page_size][d], the value
 // cache [num_pages][n_kv][page_size][dv]; v_cache == k_cache (dv <= d): a key's value is the head of its row.
@@ -263,7 +275,23 @@ PHOTON_API int photon_paged_attention(const void* q, long q_stride, void* out, l
                                       int max_pages, const int* token_seq, const int* positions, int T_,
                                       int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window,
                                       float scale, int splits, float* part, int* err, cudaStream_t stream) {
+  return photon_paged_attention_ex(q, q_stride, out, out_stride, dtype, k_cache, v_cache, block_table, max_pages, token_seq,
+                                   positions, T_, n_q, n_kv, d, dv, page_size, num_pages, window, scale, splits, part, err,
+                                   0, 0, 0.f, stream);
+}
+
+// The same with three more rules.  keep_first > 0 (with a window): keys 0 .. keep_first - 1 stay visible behind the
+// window, at their true positions.  sink != 0: the softmax has one more key with score 0 and no value, so the
+// weights of a row add up to less than one: p_j = exp(s_j) / (exp(0) + sum exp(s_i)).  softcap > 0: scores are
+// bounded, s <- softcap * tanh(s / softcap), after the scale.
+PHOTON_API int photon_paged_attention_ex(const void* q, long q_stride, void* out, long out_stride, int dtype,
+                                         const void* k_cache, const void* v_cache, const int* block_table,
+                                         int max_pages, const int* token_seq, const int* positions, int T_,
+                                         int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window,
+                                         float scale, int splits, float* part, int* err, int keep_first, int sink,
+                                         float softcap, cudaStream_t stream) {
   if (T_ <= 0) return 0;
+  if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (splits < 1 || splits > 64 || (splits > 1 && part == nullptr) || T_ > 65535 * 32) return PHOTON_ERR_ARGUMENT;
   if (splits > 1 && n_q > 65535) return PHOTON_ERR_UNSUPPORTED;
   if (n_kv <= 0 || n_q % n_kv || d <= 0 || dv <= 0 || page_size <= 0) return PHOTON_ERR_ARGUMENT;

@@ -58,10 +58,13 @@ template <> struct Quad<bf16> {
 };
 
 // VEC: rows are read and written four elements at a time (H a multiple of 4, aligned pointers).
-template <typename TD, typename TO, bool VEC>
+// CENTER: layer norm, (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b; the row's mean is taken first and the
+// squared deviations are summed in a second pass over the row held in shared memory.
+template <typename TD, typename TO, bool VEC, bool CENTER = false>
 __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* residual,   // written by earlier kernels that
                                    const void* __restrict__ w, int w_bf16,    // may still run when this one starts: no
-                                   TO* out, const int* rows, int H, float eps) {  // read-only path for them
+                                   TO* out, const int* rows, int H, float eps,   // read-only path for them
+                                   const void* __restrict__ b = nullptr, int b_bf16 = 0) {
   __shared__ float red[32];
   extern __shared__ __align__(16) float stash[];               // H floats: the summed row
   pdl_wait();
@@ -97,6 +100,15 @@ __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* res
       ss += v * v;
     }
   }
+  float mean = 0.f;
+  if (CENTER) {
+    float sm = 0.f;
+    __syncthreads();
+    for (int i = threadIdx.x; i < H; i += blockDim.x) sm += stash[i];
+    mean = block_sum(sm, red) / (float)H;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float c = stash[i] - mean; ss += c * c; }
+  }
   ss = block_sum(ss, red);
   pdl_launch_dependents();                         // the next kernel may be scheduled while the row is written
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
@@ -108,39 +120,41 @@ __global__ void add_rmsnorm_kernel(const TD* delta, const TD* delta2, float* res
       if (w_bf16) Quad<bf16>::load((const bf16*)w + i, wv); else Quad<float>::load((const float*)w + i, wv);
       if (d && !rows) Quad<float>::store(res + i, v);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) y[e] = wv[e] * (v[e] * inv);
+      for (int e = 0; e < 4; ++e) y[e] = CENTER ? (v[e] - mean) * inv * wv[e] + (b ? load_w(b, b_bf16, i + e) : 0.f) : wv[e] * (v[e] * inv);
       Quad<TO>::store(o + i, y);
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
       const float v = stash[i];
       if (d && !rows) res[i] = v;
-      o[i] = from_f32<TO>(load_w(w, w_bf16, i) * (v * inv));
+      o[i] = from_f32<TO>(CENTER ? (v - mean) * inv * load_w(w, w_bf16, i) + (b ? load_w(b, b_bf16, i) : 0.f)
+                                 : load_w(w, w_bf16, i) * (v * inv));
     }
   }
 }
 
-template <typename TD, typename TO>
+template <typename TD, typename TO, bool CENTER = false>
 static int add_rmsnorm_launch(const void* delta, const void* delta2, float* residual, const void* w, int w_bf16, void* out,
-                              const int* rows, int n, int H, float eps, cudaStream_t stream) {
+                              const int* rows, int n, int H, float eps, cudaStream_t stream,
+                              const void* b = nullptr, int b_bf16 = 0) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
   const bool vec = (H % 4 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)delta2 % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
                    ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (smem > 48 * 1024) {
-    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
+    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true, CENTER>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                        : cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>,
+                        : cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false, CENTER>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   int threads = 128;
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
   if (vec)
-    return launch_pdl(add_rmsnorm_kernel<TD, TO, true>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                      (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps);
-  return launch_pdl(add_rmsnorm_kernel<TD, TO, false>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
-                    (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps);
+    return launch_pdl(add_rmsnorm_kernel<TD, TO, true, CENTER>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
+                      (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16);
+  return launch_pdl(add_rmsnorm_kernel<TD, TO, false, CENTER>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
+                    (const TD*)delta2, residual, w, w_bf16, (TO*)out, rows, H, eps, b, b_bf16);
 }
 
 // delta may be null (plain norm); delta2 (same type as delta, may be null) is added as well: the sum of the two is
@@ -161,10 +175,29 @@ PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, const void
   return PHOTON_ERR_ARGUMENT;
 }
 
+// The same with a layer norm: out = (x - mean(x)) / sqrt(var(x) + eps) * w + b, x = residual + delta (+ delta2).
+// b may be null.
+PHOTON_API int photon_add_layernorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                                    int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows,
+                                    int n, int H, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int wb = (w_dtype == PHOTON_BF16), bb = (b_dtype == PHOTON_BF16);
+  if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
+    return add_rmsnorm_launch<bf16, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+  if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
+    return add_rmsnorm_launch<float, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+  if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
+    return add_rmsnorm_launch<float, bf16, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+  if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_F32)
+    return add_rmsnorm_launch<bf16, float, true>(delta, delta2, residual, w, wb, out, rows, n, H, eps, stream, b, bb);
+  return PHOTON_ERR_ARGUMENT;
+}
+
 // ---------------------------------------------------------------- gated activation (SwiGLU, GeGLU)
 // gate_up [T, 2*I]: columns [0, I) are the gate, [I, 2I) the up projection.  out [T, I] = act(gate) * up.
 // act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
 __device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == PHOTON_ACT_GELU) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
   if (act == PHOTON_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
 }
@@ -208,7 +241,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__
 }
 
 PHOTON_API int photon_glu(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
-  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH) return PHOTON_ERR_ARGUMENT;
+  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU) return PHOTON_ERR_ARGUMENT;
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
@@ -282,5 +315,84 @@ PHOTON_API int photon_scale_bias_rows(float* x, float scale, const void* bias, i
   const size_t cap = (size_t)photon_sm_count() * 16;
   if (blocks > cap) blocks = cap;
   scale_bias_rows_kernel<<<(int)blocks, 256, 0, stream>>>(x, scale, bias, bias_dtype == PHOTON_BF16, H, total);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- plain activation, gate, stream sums
+// out[i] = act(x[i]) over `total` elements of one dtype (x and out may be the same buffer); 32-bit arithmetic.
+template <typename T>
+__global__ void activation_kernel(const T* x, T* out, size_t total, int act) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) out[idx] = from_f32<T>(glu_act(to_f32(x[idx]), act));
+}
+
+PHOTON_API int photon_activation(const void* x, void* out, int dtype, long total, int act, cudaStream_t stream) {
+  if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU) return PHOTON_ERR_ARGUMENT;
+  if (total <= 0) return 0;
+  size_t blocks = ((size_t)total + 255) / 256;
+  const size_t cap = (size_t)photon_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (dtype == PHOTON_BF16) activation_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)x, (bf16*)out, (size_t)total, act);
+  else activation_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)total, act);
+  return launch_status();
+}
+
+// x [T, W] (row stride ldx, in place) *= sigmoid(g [T, W]) (row stride ldg; its own type): the gate of a mixer's
+// output.  The sigmoid and the product are 32-bit, the result is rounded once.
+template <typename TX, typename TG>
+__global__ void gate_mul_kernel(TX* x, long ldx, const TG* g, long ldg, int W, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const size_t t = idx / W;
+    const int i = (int)(idx - t * W);
+    const float z = to_f32(g[t * ldg + i]);
+    x[t * ldx + i] = from_f32<TX>(to_f32(x[t * ldx + i]) / (1.0f + expf(-z)));
+  }
+}
+
+PHOTON_API int photon_gate_mul(void* x, long ldx, int x_dtype, const void* g, long ldg, int g_dtype, int T, int W,
+                               cudaStream_t stream) {
+  const size_t total = (size_t)T * W;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = (size_t)photon_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_BF16) gate_mul_kernel<bf16, bf16><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const bf16*)g, ldg, W, total);
+  else if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_F32) gate_mul_kernel<bf16, float><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const float*)g, ldg, W, total);
+  else if (x_dtype == PHOTON_F32 && g_dtype == PHOTON_F32) gate_mul_kernel<float, float><<<(int)blocks, 256, 0, stream>>>((float*)x, ldx, (const float*)g, ldg, W, total);
+  else return PHOTON_ERR_ARGUMENT;
+  return launch_status();
+}
+
+// residual [T, H] (float, in place) += (delta + delta2) + other + bias: what is pending on the stream, a second
+// stream of the same width (may be null) and one vector for all rows (may be null), each term added in 32-bit in
+// this order.
+template <typename TD>
+__global__ void stream_add_kernel(float* residual, const TD* delta, const TD* delta2, const float* other,
+                                  const void* bias, int bias_bf16, int H, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    float v = residual[idx];
+    if (delta) v += delta2 ? to_f32(delta[idx]) + to_f32(delta2[idx]) : to_f32(delta[idx]);
+    if (other) v += other[idx];
+    if (bias) v += load_w(bias, bias_bf16, idx % H);
+    residual[idx] = v;
+  }
+}
+
+PHOTON_API int photon_stream_add(float* residual, const void* delta, const void* delta2, int delta_dtype, const float* other,
+                                 const void* bias, int bias_dtype, int T, int H, cudaStream_t stream) {
+  const size_t total = (size_t)T * H;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = (size_t)photon_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (delta_dtype == PHOTON_BF16)
+    stream_add_kernel<bf16><<<(int)blocks, 256, 0, stream>>>(residual, (const bf16*)delta, (const bf16*)delta2, other, bias, bias_dtype == PHOTON_BF16, H, total);
+  else
+    stream_add_kernel<float><<<(int)blocks, 256, 0, stream>>>(residual, (const float*)delta, (const float*)delta2, other, bias, bias_dtype == PHOTON_BF16, H, total);
   return launch_status();
 }

@@ -22,16 +22,18 @@
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ Wr,
                                  const void* __restrict__ bias, int bias_bf16, int H, int E, int top,
-                                 int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T_) {
-  extern __shared__ float logits[];                     // E
+                                 int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T_,
+                                 int mode, int n_groups, int keep_groups, float route_scale,
+                                 const T* __restrict__ Wsg, float* __restrict__ shared_gate) {
+  extern __shared__ float logits[];                     // E (+ 1: the logit of the shared expert's gate)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   const int t = blockIdx.x;                              // one block per token, its warps share the experts out
   float* lg = logits;
   const T* x = h + (size_t)t * h_stride;
   constexpr int V = 16 / sizeof(T);                      // elements of a 16-byte load
   const bool vec = (H % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)Wr % 16 == 0);
-  for (int e = warp; e < E; e += nwarp) {
-    const T* w = Wr + (size_t)e * H;
+  for (int e = warp; e < E + (Wsg ? 1 : 0); e += nwarp) {
+    const T* w = e < E ? Wr + (size_t)e * H : Wsg;
     float acc = 0.f;
     if (vec) {
       for (int k = lane * V; k < H; k += 32 * V) {
@@ -45,10 +47,55 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
       for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(x[k]), to_f32(w[k]), acc);
     }
     acc = warp_sum(acc);
-    if (lane == 0) lg[e] = acc + (bias ? load_w(bias, bias_bf16, e) : 0.f);
+    if (lane == 0) lg[e] = acc + ((bias && e < E) ? load_w(bias, bias_bf16, e) : 0.f);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && Wsg) shared_gate[t] = 1.0f / (1.0f + expf(-lg[E]));
+  if (threadIdx.x == 0 && mode == 1) {
+    // scores: softmax over ALL experts.  Groups of E / n_groups neighbours: a group's score is its largest score,
+    // and only experts of the keep_groups best groups can be chosen.  Weights: the chosen scores over their sum,
+    // times route_scale.  Ties go to the lower index everywhere.
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
+    float den = 0.f;
+    for (int e = 0; e < E; ++e) { const float p = expf(lg[e] - mx); lg[e] = p; den += p; }
+    for (int e = 0; e < E; ++e) lg[e] /= den;
+    if (n_groups > 1 && keep_groups < n_groups) {
+      const int per = E / n_groups;
+      unsigned long long kept = 0ull;                    // n_groups <= 64
+      for (int r = 0; r < keep_groups; ++r) {
+        int bg = -1;
+        float bs = -1.f;
+        for (int g = 0; g < n_groups; ++g) {
+          if (kept >> g & 1ull) continue;
+          float gs = -1.f;
+          for (int i = 0; i < per; ++i) gs = fmaxf(gs, lg[g * per + i]);
+          if (gs > bs) { bs = gs; bg = g; }
+        }
+        kept |= 1ull << bg;
+      }
+      // a score of an expert outside the kept groups is hidden behind a negative number; it is not used again
+      for (int g = 0; g < n_groups; ++g)
+        if (!(kept >> g & 1ull))
+          for (int i = 0; i < per; ++i) lg[g * per + i] = -1.f;
+    }
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int e = 0; e < E; ++e) {
+        const float v = lg[e];
+        if (v > bv) { bv = v; best = e; }
+      }
+      ids[(size_t)t * top + j] = best;
+      weights[(size_t)t * top + j] = bv;
+      sum += bv;
+      lg[best] = -2.f;
+      atomicAdd(&counts[best], 1);
+    }
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = weights[(size_t)t * top + j] / (sum + 1e-20f) * route_scale;
+  }
+  if (threadIdx.x == 0 && mode == 0) {
     float chosen_max = -INFINITY;
     for (int j = 0; j < top; ++j) {
       int best = -1;
@@ -78,20 +125,39 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
 PHOTON_API int photon_moe_route(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype,
                                 int T_, int H, int E, int top, int* ids, float* weights, int* counts,
                                 cudaStream_t stream) {
+  return photon_moe_route_ex(h, h_stride, dtype, Wr, bias, bias_dtype, T_, H, E, top, ids, weights, counts, 0, 1, 1, 1.0f,
+                             nullptr, nullptr, stream);
+}
+
+// mode 0: as above.  mode 1: scores are the softmax over all experts; with n_groups > 1 the experts form that many
+// equal groups of neighbours and only experts of the keep_groups groups with the largest best score can be chosen; the
+// weights are the chosen scores divided by their sum (+ 1e-20) times route_scale.  Wsg (may be null): one more row
+// [H] of the router's type; shared_gate [T] then gets sigmoid(Wsg . h), the gate of a shared expert.
+PHOTON_API int photon_moe_route_ex(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype,
+                                   int T_, int H, int E, int top, int* ids, float* weights, int* counts, int mode,
+                                   int n_groups, int keep_groups, float route_scale, const void* Wsg, float* shared_gate,
+                                   cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || H <= 0) return PHOTON_ERR_ARGUMENT;
+  if (mode != 0 && mode != 1) return PHOTON_ERR_ARGUMENT;
+  if (n_groups < 1 || keep_groups < 1 || keep_groups > n_groups || E % n_groups) return PHOTON_ERR_ARGUMENT;
+  if (n_groups > 64) return PHOTON_ERR_UNSUPPORTED;
+  if (mode == 1 && n_groups > 1 && (long)keep_groups * (E / n_groups) < top) return PHOTON_ERR_ARGUMENT;
+  if ((Wsg == nullptr) != (shared_gate == nullptr)) return PHOTON_ERR_ARGUMENT;
   const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
-  const size_t smem = (size_t)E * sizeof(float);
+  const size_t smem = (size_t)(E + 1) * sizeof(float);
   if (smem > 48 * 1024) return PHOTON_ERR_UNSUPPORTED;
   cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
   const int blocks = T_;
   if (dtype == PHOTON_BF16)
     moe_route_kernel<bf16><<<blocks, warps * 32, smem, stream>>>((const bf16*)h, h_stride, (const bf16*)Wr, bias,
-                                                                bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_);
+                                                                bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_,
+                                                                mode, n_groups, keep_groups, route_scale, (const bf16*)Wsg, shared_gate);
   else
     moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>((const float*)h, h_stride, (const float*)Wr, bias,
-                                                                 bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_);
+                                                                 bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_,
+                                                                 mode, n_groups, keep_groups, route_scale, (const float*)Wsg, shared_gate);
   return launch_status();
 }
 
@@ -152,6 +218,8 @@ PHOTON_API int photon_moe_tile_rows(void) { return MOE_BM; }
 #define MOE_BK 16
 
 __device__ __forceinline__ float moe_act(float g, int act) {
+  if (act == PHOTON_ACT_NONE) return g;
+  if (act == PHOTON_ACT_GELU) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
   if (act == PHOTON_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
 }
@@ -226,7 +294,7 @@ moe_gemm_kernel(const T* __restrict__ A, long lda, const int* __restrict__ gathe
       const int gn = n0 + tx * 4 + j;
       if (gn >= cols) continue;
       float v = acc[0][i][j];
-      if (GLU) v = moe_act(v, act) * acc[GLU ? 1 : 0][i][j];
+      v = GLU ? moe_act(v, act) * acc[GLU ? 1 : 0][i][j] : moe_act(v, act);
       out[(size_t)(r0 + row) * ldo + gn] = from_f32<TO>(v);
     }
   }
@@ -234,6 +302,7 @@ moe_gemm_kernel(const T* __restrict__ A, long lda, const int* __restrict__ gathe
 
 // A [*][K] (row stride lda).  gather (may be null): row r of the sorted order reads A row gather[r] / gather_div;
 // null: row r itself.  W [E][N][K] contiguous.  out [n][N] (or [n][N / 2] with glu != 0), rows in sorted order.
+// act: PHOTON_ACT_*; with glu != 0 it is applied to the gate, otherwise to every output (PHOTON_ACT_NONE: plain product).
 // out_dtype: PHOTON_F32 or the input type.  max_tiles: bound of the tile list (the grid's height).
 PHOTON_API int photon_moe_gemm(const void* A, long lda, int dtype, const int* gather, int gather_div, const void* W,
                                void* out, long ldo, int out_dtype, int N, int K, const int* tiles, const int* num_tiles,
@@ -256,14 +325,14 @@ PHOTON_API int photon_moe_gemm(const void* A, long lda, int dtype, const int* ga
 template <typename TY, typename TO>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, long ldy, const int* __restrict__ place,
                                    const float* __restrict__ weights, int top, const TO* __restrict__ shared_out,
-                                   TO* __restrict__ out, int H) {
+                                   TO* __restrict__ out, int H, const float* __restrict__ shared_gate) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
       acc = fmaf(weights[(size_t)t * top + j],
                  to_f32(y[(size_t)(place ? place[(size_t)t * top + j] : t * top + j) * ldy + i]), acc);
-    if (shared_out) acc += to_f32(shared_out[(size_t)t * H + i]);
+    if (shared_out) acc += shared_gate ? shared_gate[t] * to_f32(shared_out[(size_t)t * H + i]) : to_f32(shared_out[(size_t)t * H + i]);
     out[(size_t)t * H + i] = from_f32<TO>(acc);
   }
 }
@@ -272,14 +341,21 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, long ldy, const int
 // weights [T][top]; shared_out [T][H] (may be null) and out [T][H] of out_dtype.
 PHOTON_API int photon_moe_combine(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
                                   const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream) {
+  return photon_moe_combine_ex(y, ldy, y_dtype, place, weights, top, shared_out, nullptr, out, out_dtype, T_, H, stream);
+}
+
+// The same; shared_gate [T] (may be null): the shared expert's output of token t is multiplied by shared_gate[t].
+PHOTON_API int photon_moe_combine_ex(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
+                                     const void* shared_out, const float* shared_gate, void* out, int out_dtype, int T_,
+                                     int H, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (out_dtype == PHOTON_BF16 && y_dtype == PHOTON_F32)
-    moe_combine_kernel<float, bf16><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+    moe_combine_kernel<float, bf16><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H, shared_gate);
   else if (out_dtype == PHOTON_BF16 && y_dtype == PHOTON_BF16)
-    moe_combine_kernel<bf16, bf16><<<T_, threads, 0, stream>>>((const bf16*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H);
+    moe_combine_kernel<bf16, bf16><<<T_, threads, 0, stream>>>((const bf16*)y, ldy, place, weights, top, (const bf16*)shared_out, (bf16*)out, H, shared_gate);
   else if (out_dtype == PHOTON_F32 && y_dtype == PHOTON_F32)
-    moe_combine_kernel<float, float><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const float*)shared_out, (float*)out, H);
+    moe_combine_kernel<float, float><<<T_, threads, 0, stream>>>((const float*)y, ldy, place, weights, top, (const float*)shared_out, (float*)out, H, shared_gate);
   else
     return PHOTON_ERR_ARGUMENT;
   return launch_status();
@@ -360,7 +436,7 @@ moe_gemv_kernel(const bf16* __restrict__ x, long ldx, int x_div, const int* __re
     }
     a0 = warp_sum(a0);
     if (GLU) a1 = warp_sum(a1);
-    if (lane == 0) out[(size_t)p * ldo + col] = from_f32<TO>(GLU ? moe_act(a0, act) * a1 : a0);
+    if (lane == 0) out[(size_t)p * ldo + col] = from_f32<TO>(GLU ? moe_act(a0, act) * a1 : moe_act(a0, act));
   }
 }
 

@@ -71,7 +71,7 @@ def pages_for(model: CausalLM, options: EngineOptions, max_model_len: int) -> Li
     def cap(spec) -> Optional[int]:
         if spec.window is None:
             return None
-        per_request = -(-(spec.window + min(options.max_num_batched_tokens, max_model_len)) // ps) + 1
+        per_request = -(-(spec.window + min(options.max_num_batched_tokens, max_model_len)) // ps) + 1 + -(-spec.keep_first // ps)
         return options.max_sequences * per_request
 
     def capped(n: int) -> List[int]:
@@ -82,7 +82,7 @@ def pages_for(model: CausalLM, options: EngineOptions, max_model_len: int) -> Li
     if options.max_cache_tokens is not None:
         return capped((options.max_cache_tokens + ps - 1) // ps)
     es = torch.empty((), dtype=model.dtype).element_size()
-    page_bytes = [len(entries) * s.planes * s.n_kv_heads * s.head_dim * es * ps for s, entries in specs]
+    page_bytes = [len(entries) * s.n_kv_heads * s.row_width * es * ps for s, entries in specs]
     free, _total = torch.cuda.mem_get_info(model.device)
     budget = int(free * options.gpu_memory_fraction)
     # no more than every live request at full length, and no more than 2^20 tokens unless asked for

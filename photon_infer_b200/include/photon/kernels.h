@@ -52,6 +52,8 @@ extern "C" {
 /* activations of the gated feed-forward kernels: silu, and the tanh form of gelu */
 #define PHOTON_ACT_SILU 0
 #define PHOTON_ACT_GELU_TANH 1
+#define PHOTON_ACT_GELU 2            /* the exact form, 0.5 z (1 + erf(z / sqrt 2)) */
+#define PHOTON_ACT_NONE (-1)
 
 /* ------------------------------------------------------------------ elementwise.cu */
 /* out[t, :] = table[ids[t], :] as float; ids outside [0, V) give a zero row and PHOTON_DEV_BAD_TOKEN. */
@@ -62,6 +64,10 @@ PHOTON_EXPORT int photon_embedding(const int* ids, const void* table, int table_
  * rows (may be null): only these rows are read, nothing is written back, out has one row per entry. */
 PHOTON_EXPORT int photon_add_rmsnorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
                        int w_dtype, void* out, int out_dtype, const int* rows, int n, int H, float eps, cudaStream_t stream);
+/* The same with a layer norm: out = (x - mean(x)) / sqrt(var(x) + eps) * w + b, x = residual + delta (+ delta2); b may be null. */
+PHOTON_EXPORT int photon_add_layernorm(const void* delta, int delta_dtype, const void* delta2, float* residual, const void* w,
+                         int w_dtype, const void* b, int b_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                         float eps, cudaStream_t stream);
 /* out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I] of one dtype; act: PHOTON_ACT_*.
  * photon_swiglu is photon_glu with silu. */
 PHOTON_EXPORT int photon_glu(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream);
@@ -71,6 +77,14 @@ PHOTON_EXPORT int photon_stream_concat(const float* residual, const void* delta,
                          const float* other, void* out, int out_dtype, int T, int H, cudaStream_t stream);
 /* x [T, H] (float, in place) = x * scale + bias; bias [H] of bias_dtype, may be null. */
 PHOTON_EXPORT int photon_scale_bias_rows(float* x, float scale, const void* bias, int bias_dtype, int T, int H, cudaStream_t stream);
+/* out[i] = act(x[i]) over total elements of one dtype (x may be out); act: PHOTON_ACT_SILU, _GELU_TANH or _GELU. */
+PHOTON_EXPORT int photon_activation(const void* x, void* out, int dtype, long total, int act, cudaStream_t stream);
+/* x [T, W] (row stride ldx, in place) *= sigmoid(g [T, W]) (row stride ldg, its own dtype), in 32-bit, rounded once. */
+PHOTON_EXPORT int photon_gate_mul(void* x, long ldx, int x_dtype, const void* g, long ldg, int g_dtype, int T, int W, cudaStream_t stream);
+/* residual [T, H] (float, in place) += (delta + delta2) + other + bias; delta, delta2 [T, H] of delta_dtype, other [T, H]
+ * float, bias [H] of bias_dtype; each may be null. */
+PHOTON_EXPORT int photon_stream_add(float* residual, const void* delta, const void* delta2, int delta_dtype, const float* other,
+                      const void* bias, int bias_dtype, int T, int H, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ rope_kv.cu */
 /* Rotates q [T, n_q * d] and k [T, n_kv * d] in place (rotate != 0; pairs (2j, 2j+1) when interleaved, else
@@ -83,6 +97,17 @@ PHOTON_EXPORT int photon_rope_kv_write(void* q, long q_stride, void* k, long k_s
 /* out [count][half][2] float: (cos, sin) of position * inv_freq[j]. */
 PHOTON_EXPORT int photon_rope_table(const float* inv_freq, int half, int count, void* out, cudaStream_t stream);
 
+/* ------------------------------------------------------------------ qk_norm.cu */
+/* Per head: y = x / sqrt(mean(x^2) + eps) [* w], then the first rot_dims numbers rotated in halves (number j with number
+ * j + rot_dims / 2) by position * inv_freq[j] (double [rot_dims / 2]; null: no rotation); queries to q_out (out_dtype),
+ * keys and values (dv wide) into their caches at slot_mapping (slot -1: nothing stored; both caches null: only queries).
+ * in_dtype may be PHOTON_F32 while out_dtype is PHOTON_BF16. */
+PHOTON_EXPORT int photon_qk_norm_rope_write(const void* q, long q_stride, const void* k, long k_stride, const void* v, long v_stride,
+                              int in_dtype, void* q_out, long qo_stride, int out_dtype, const void* q_w, const void* k_w,
+                              int w_dtype, float eps, const int* positions, const double* inv_freq, int rot_dims,
+                              const int* slot_mapping, void* k_cache, void* v_cache, int T, int n_q, int n_kv, int d, int dv,
+                              int page_size, long num_slots, int* err, cudaStream_t stream);
+
 /* ------------------------------------------------------------------ attention.cu (float32 and any even head size) */
 /* Values are dv wide: v_cache [num_pages][n_kv][page_size][dv], out [T][n_q * dv]; v_cache == k_cache (dv <= d): the value
  * of a key is the head of its own row (attention over a cached latent).  splits > 1: every token's key tiles are shared out
@@ -91,6 +116,13 @@ PHOTON_EXPORT int photon_paged_attention(const void* q, long q_stride, void* out
                            const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                            const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
                            int window, float scale, int splits, float* part, int* err, cudaStream_t stream);
+/* The same with kept first keys (keys < keep_first stay visible behind the window), a sink (one more key with score 0 and
+ * no value in the softmax's denominator) and bounded scores (s <- softcap * tanh(s / softcap); 0: off). */
+PHOTON_EXPORT int photon_paged_attention_ex(const void* q, long q_stride, void* out, long out_stride, int dtype, const void* k_cache,
+                              const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
+                              const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
+                              int window, float scale, int splits, float* part, int* err, int keep_first, int sink,
+                              float softcap, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ latent.cu: attention over a cached latent */
 /* One pass over a token's fused down-projection row down[t] = [query latent (q_rank) | key/value latent (kv_rank) |
@@ -151,6 +183,12 @@ PHOTON_EXPORT int photon_gla_chunked(const void* q, const void* k, const void* v
  * counts [E]: pairs per expert. */
 PHOTON_EXPORT int photon_moe_route(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype, int T_,
                      int H, int E, int top, int* ids, float* weights, int* counts, cudaStream_t stream);
+/* mode 1: softmax over all experts, groups of neighbours of which only the keep_groups best (by their largest score) may
+ * be chosen from, weights = chosen scores / (their sum + 1e-20) * route_scale.  Wsg [H] (may be null): shared_gate [T] =
+ * sigmoid(Wsg . h). */
+PHOTON_EXPORT int photon_moe_route_ex(const void* h, long h_stride, int dtype, const void* Wr, const void* bias, int bias_dtype, int T_,
+                        int H, int E, int top, int* ids, float* weights, int* counts, int mode, int n_groups, int keep_groups,
+                        float route_scale, const void* Wsg, float* shared_gate, cudaStream_t stream);
 /* Stable sort of the n = T * top pairs by expert: offsets [E + 1], sorted [n], place [n], tiles [3 * max_tiles] of
  * photon_moe_tile_rows() rows at most (expert, first row, rows), num_tiles [1]. */
 PHOTON_EXPORT int photon_moe_align(const int* ids, const int* counts, int n, int E, int* offsets, int* sorted, int* place,
@@ -164,6 +202,10 @@ PHOTON_EXPORT int photon_moe_gemm(const void* A, long lda, int dtype, const int*
 /* out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t]); y [n][H] float or bfloat16; place null: row t * top + j. */
 PHOTON_EXPORT int photon_moe_combine(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
                        const void* shared_out, void* out, int out_dtype, int T_, int H, cudaStream_t stream);
+/* shared_gate [T] (may be null) multiplies the shared expert's rows. */
+PHOTON_EXPORT int photon_moe_combine_ex(const void* y, long ldy, int y_dtype, const int* place, const float* weights, int top,
+                          const void* shared_out, const float* shared_gate, void* out, int out_dtype, int T_, int H,
+                          cudaStream_t stream);
 /* out[r, :] = x[sorted[r] / div, :]: the pairs' input rows in sorted order. */
 PHOTON_EXPORT int photon_moe_gather(const void* x, long ldx, int dtype, const int* sorted, int div, void* out, int n, int H,
                       cudaStream_t stream);

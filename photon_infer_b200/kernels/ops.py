@@ -135,7 +135,84 @@ def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: t
            "add_rmsnorm")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}     # gelu: the exact (erf) form
+ACT_NONE = -1
+
+
+def add_layernorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                  eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                  delta2: Optional[torch.Tensor] = None) -> None:
+    """As ``add_rmsnorm`` with a layer norm: ``out = (x - mean(x)) / sqrt(var(x) + eps) * weight + bias`` with
+    ``x = residual + delta (+ delta2)``, all in 32-bit; the variance is the mean of the squared deviations."""
+    _cuda(delta, residual, weight, bias, out, rows, delta2)
+    if delta2 is not None:
+        if delta is None:
+            delta, delta2 = delta2, None
+        elif delta2.shape != delta.shape or delta2.dtype != delta.dtype or not delta2.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_layernorm: delta2 must match delta")
+    H = residual.shape[-1]
+    n = rows.numel() if rows is not None else residual.shape[0]
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "add_layernorm: the residual stream must be contiguous float32")
+    if delta is not None and (delta.shape != residual.shape or not delta.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_layernorm: delta must match the residual stream")
+    if out.shape != (n, H) or not out.is_contiguous() or weight.numel() != H or (bias is not None and bias.numel() != H):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_layernorm: out must be [rows, H], weight and bias [H]")
+    if rows is not None:
+        _int32(rows, "rows")
+    f = _fn("elementwise", "photon_add_layernorm",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+             c_float, c_void_p])
+    _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(delta2), _ptr(residual), _ptr(weight),
+             _dtype_code(weight), _ptr(bias), _dtype_code(bias) if bias is not None else F32, _ptr(out), _dtype_code(out),
+             _ptr(rows), n, H, float(eps), _stream()), "add_layernorm")
+
+
+def activation(x: torch.Tensor, activation: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(x)`` element by element (in place unless ``out`` is given), 32-bit arithmetic."""
+    _cuda(x, out)
+    if activation not in ACTIVATIONS:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"unknown activation {activation!r} ({', '.join(ACTIVATIONS)})")
+    out = x if out is None else out
+    if not x.is_contiguous() or not out.is_contiguous() or out.shape != x.shape or out.dtype != x.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "activation: x and out contiguous, of one shape and dtype")
+    f = _fn("elementwise", "photon_activation", [c_void_p, c_void_p, c_int, c_long, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(out), _dtype_code(x), x.numel(), ACTIVATIONS[activation], _stream()), "activation")
+    return out
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """``x [T, W] *= sigmoid(gate [T, W])`` in place; both may be views with a row stride, ``gate`` may be 32-bit
+    beside a bfloat16 ``x``."""
+    _cuda(x, gate)
+    if x.dim() != 2 or gate.shape != x.shape or x.stride(1) != 1 or gate.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gate_mul: x and gate [T, W] with contiguous rows")
+    f = _fn("elementwise", "photon_gate_mul", [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _dtype_code(x), _ptr(gate), gate.stride(0), _dtype_code(gate), x.shape[0], x.shape[1],
+             _stream()), "gate_mul")
+
+
+def stream_add(residual: torch.Tensor, delta: Optional[torch.Tensor], delta2: Optional[torch.Tensor],
+               other: Optional[torch.Tensor], bias: Optional[torch.Tensor]) -> None:
+    """``residual += (delta + delta2) + other + bias`` in 32-bit, in place: what is pending on the stream, a second
+    32-bit stream of the same shape and one vector ``[H]`` for all rows; each may be None."""
+    _cuda(residual, delta, delta2, other, bias)
+    T, H = residual.shape
+    if delta is None and delta2 is not None:
+        delta, delta2 = delta2, None
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "stream_add: the residual stream must be contiguous float32")
+    for t in (delta, delta2):
+        if t is not None and (t.shape != residual.shape or not t.is_contiguous() or t.dtype != delta.dtype):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_add: pending outputs must match the residual stream")
+    if other is not None and (other.shape != residual.shape or other.dtype != torch.float32 or not other.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_add: the second stream must be contiguous float32 [T, H]")
+    if bias is not None and (bias.numel() != H or not bias.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "stream_add: bias must be [H]")
+    f = _fn("elementwise", "photon_stream_add",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _ptr(delta2), _dtype_code(delta) if delta is not None else F32, _ptr(other),
+             _ptr(bias), _dtype_code(bias) if bias is not None else F32, T, H, _stream()), "stream_add")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
@@ -239,18 +316,72 @@ def rope_kv_write(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optio
              page_size, num_slots, int(rotate), int(write), _ptr(err), _stream()), "rope_kv_write")
 
 
+def qk_norm_rope_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_out: torch.Tensor,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                       slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                       v_cache: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, value_dim: int,
+                       err: Optional[torch.Tensor]) -> None:
+    """Per head ``y = x / sqrt(mean(x^2) + eps) [* weight]`` for ``q [T, n_q * d]`` and ``k [T, n_kv * d]``, then the
+    rotation of the first ``rot_dims`` numbers of every head (number ``j`` with ``j + rot_dims / 2``, angle
+    ``position * inv_freq[j]``, ``inv_freq`` float64), queries into ``q_out`` and keys and ``v [T, n_kv * dv]`` into the
+    paged caches ``[pages, n_kv, page_size, d | dv]``.  The inputs are views with any row stride and may be 32-bit
+    while ``q_out`` and the caches are bfloat16.  Caches None: only the queries (``k`` and ``v`` are not read)."""
+    _cuda(q, k, v, q_out, q_weight, k_weight, positions, inv_freq, slot_mapping, k_cache, v_cache, err)
+    T = q.shape[0]
+    d, dv = head_dim, value_dim
+    if q.shape != (T, n_q * d) or q.stride(1) != 1 or q_out.shape != (T, n_q * d) or q_out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "qk_norm_rope_write: q and q_out must be [T, n_q * head_dim]")
+    write = k_cache is not None
+    page_size, num_slots = 1, 0
+    if write:
+        if k is None or v is None or k.shape != (T, n_kv * d) or v.shape != (T, n_kv * dv) or k.stride(1) != 1 \
+                or v.stride(1) != 1 or k.dtype != q.dtype or v.dtype != q.dtype:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "qk_norm_rope_write: k [T, n_kv * head_dim], v [T, n_kv * value_dim]")
+        _int32(slot_mapping, "slot_mapping")
+        if k_cache.dim() != 4 or k_cache.shape[1] != n_kv or k_cache.shape[3] != d or v_cache.shape[:3] != k_cache.shape[:3] \
+                or v_cache.shape[3] != dv or k_cache.dtype != q_out.dtype or v_cache.dtype != q_out.dtype \
+                or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH,
+                              "qk_norm_rope_write: caches must be contiguous [pages, n_kv, page_size, head_dim | value_dim]")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    _int32(positions, "positions")
+    if inv_freq is not None and (inv_freq.dtype != torch.float64 or inv_freq.numel() != rot_dims // 2 or rot_dims % 2
+                                 or rot_dims > d):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "qk_norm_rope_write: inv_freq must be float64 [rot_dims / 2], rot_dims even, <= head_dim")
+    wt = q_weight if q_weight is not None else k_weight
+    for w in (q_weight, k_weight):
+        if w is not None and (w.numel() != d or w.dtype != wt.dtype or not w.is_contiguous()):
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "qk_norm_rope_write: norm weights must be [head_dim] of one dtype")
+    f = _fn("qk_norm", "photon_qk_norm_rope_write",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int,
+             c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_long, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(k) if write else None, k.stride(0) if write else 0, _ptr(v) if write else None,
+             v.stride(0) if write else 0, _dtype_code(q), _ptr(q_out), q_out.stride(0), _dtype_code(q_out), _ptr(q_weight),
+             _ptr(k_weight), _dtype_code(wt) if wt is not None else F32, float(eps), _ptr(positions),
+             _ptr(inv_freq) if rot_dims else None, int(rot_dims) if inv_freq is not None else 0, _ptr(slot_mapping),
+             _ptr(k_cache), _ptr(v_cache), T, n_q, n_kv, d, dv, page_size, num_slots, _ptr(err), _stream()),
+           "qk_norm_rope_write")
+
+
 # ----------------------------------------------------------------------------- attention
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float,
-                    err: Optional[torch.Tensor], value_dim: Optional[int] = None, splits: int = 1) -> None:
+                    err: Optional[torch.Tensor], value_dim: Optional[int] = None, splits: int = 1,
+                    keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None) -> None:
     """General paged causal attention.  ``q`` is a ``[T, n_q * d]`` view (row stride free),
     ``out [T, n_q * dv]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
     ``max(0, p - window + 1) .. p`` through ``block_table[seq]``.  ``value_dim`` (default ``head_dim``) is the
     width of a value; ``v_cache is k_cache`` means that a key's value is the first ``value_dim`` numbers of
     its own row (attention over a cached latent).  ``splits`` > 1 shares every token's keys out over that many
-    blocks (for decoded tokens with long contexts; the order of the sums then depends on ``splits``)."""
+    blocks (for decoded tokens with long contexts; the order of the sums then depends on ``splits``).
+    ``keep_first``: with a window, keys ``0 .. keep_first - 1`` stay visible as well.  ``sink``: the softmax has one
+    more key with score 0 and no value (``p_j = exp(s_j) / (1 + sum exp(s_i))``).  ``softcap``: scores become
+    ``softcap * tanh(score / softcap)`` after the scale."""
     _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
     T = q.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
@@ -266,15 +397,16 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "paged_attention: the caches' last dimension must be head_dim / value_dim")
     for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
         _int32(t, name)
-    f = _fn("attention", "photon_paged_attention",
+    f = _fn("attention", "photon_paged_attention_ex",
             [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_float, c_void_p])
     splits = max(1, min(int(splits), 64))
     part = torch.empty(T * n_q * splits * (dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim, dv,
              k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), splits, _ptr(part), _ptr(err),
-             _stream()), "paged_attention")
+             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "paged_attention")
     if splits > 1:
         global _launch_count
         _launch_count += 1
@@ -1026,10 +1158,19 @@ def moe_tile_rows() -> int:
     return int(load_module("moe").photon_moe_tile_rows())
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
-    """Router logits in 32-bit, the ``top`` experts of every token and the softmax over their logits.  Returns
-    ``(ids int32 [T, top], weights float32 [T, top], counts int32 [E])``."""
-    _cuda(h, w_router, bias)
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+              scoring: str = "softmax_chosen", groups: int = 1, keep_groups: int = 1, route_scale: float = 1.0,
+              w_shared_gate: Optional[torch.Tensor] = None):
+    """Router logits in 32-bit and the ``top`` experts of every token.  ``scoring`` ``softmax_chosen``: the largest
+    logits win and the weights are the softmax over the chosen logits.  ``softmax_all``: scores are the softmax
+    over all experts; the experts form ``groups`` equal groups of neighbours, a group's score is its largest
+    score and only experts of the ``keep_groups`` best groups can be chosen; the weights are the chosen scores
+    over their sum (+ 1e-20) times ``route_scale``.  ``w_shared_gate [1, H]``: also returns ``sigmoid(w . h)``
+    per token.  Returns ``(ids int32 [T, top], weights float32 [T, top], counts int32 [E])`` or, with a gate,
+    those and ``gate float32 [T]``."""
+    _cuda(h, w_router, bias, w_shared_gate)
+    if scoring not in ROUTER_SCORING:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"moe_route: unknown scoring {scoring!r} ({', '.join(ROUTER_SCORING)})")
     T, H = h.shape
     E = w_router.shape[0]
     if w_router.shape != (E, H) or not w_router.is_contiguous() or h.stride(1) != 1 or h.dtype != w_router.dtype:
@@ -1037,13 +1178,24 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
     counts = torch.empty(E, dtype=torch.int32, device=h.device)
-    f = _fn("moe", "photon_moe_route",
+    gate = None
+    if w_shared_gate is not None:
+        if w_shared_gate.numel() != H or w_shared_gate.dtype != w_router.dtype or not w_shared_gate.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_route: the shared expert's gate must be [1, H] of the router's dtype")
+        gate = torch.empty(T, dtype=torch.float32, device=h.device)
+    f = _fn("moe", "photon_moe_route_ex",
             [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(h), h.stride(0), _dtype_code(h), _ptr(w_router), _ptr(bias),
              _dtype_code(bias) if bias is not None else F32, T, H, E, int(top), _ptr(ids), _ptr(weights), _ptr(counts),
+             ROUTER_SCORING[scoring], int(groups), int(keep_groups), float(route_scale), _ptr(w_shared_gate), _ptr(gate),
              _stream()), "moe_route")
+    if gate is not None:
+        return ids, weights, counts, gate
     return ids, weights, counts
+
+
+ROUTER_SCORING = {"softmax_chosen": 0, "softmax_all": 1}
 
 
 def moe_align(ids: torch.Tensor, counts: torch.Tensor):
@@ -1067,11 +1219,13 @@ def moe_align(ids: torch.Tensor, counts: torch.Tensor):
 
 def moe_gemm(a: torch.Tensor, gather: Optional[torch.Tensor], gather_div: int, weight: torch.Tensor, out: torch.Tensor,
              tiles: torch.Tensor, num_tiles: torch.Tensor, max_tiles: int, glu: bool = False,
-             activation: str = "silu") -> None:
+             activation: Optional[str] = None) -> None:
     """Grouped product over rows sorted by expert: ``weight [E, N, K]``; sorted row ``r`` reads row
     ``gather[r] // gather_div`` of ``a`` (``gather`` None: row ``r``).  ``glu``: ``weight`` holds gate rows
-    then up rows and ``out [n, N / 2] = act(gate) * up``."""
+    then up rows and ``out [n, N / 2] = act(gate) * up`` (silu unless named).  Without ``glu`` an ``activation`` is
+    applied to every output (None: the plain product)."""
     _cuda(a, gather, weight, out, tiles, num_tiles)
+    act = ACTIVATIONS[activation or "silu"] if glu or activation else ACT_NONE
     E, N, K = weight.shape
     if a.shape[1] != K or a.stride(1) != 1 or not weight.is_contiguous() or a.dtype != weight.dtype \
             or out.stride(1) != 1 or out.shape[1] != (N // 2 if glu else N) or out.dtype not in (a.dtype, torch.float32):
@@ -1080,25 +1234,28 @@ def moe_gemm(a: torch.Tensor, gather: Optional[torch.Tensor], gather_div: int, w
             [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p,
              c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(a), a.stride(0), _dtype_code(a), _ptr(gather), int(gather_div), _ptr(weight), _ptr(out), out.stride(0),
-             _dtype_code(out), N, K, _ptr(tiles), _ptr(num_tiles), int(max_tiles), int(glu), ACTIVATIONS[activation],
+             _dtype_code(out), N, K, _ptr(tiles), _ptr(num_tiles), int(max_tiles), int(glu), act,
              _stream()), "moe_gemm")
 
 
 def moe_combine(y: torch.Tensor, place: Optional[torch.Tensor], weights: torch.Tensor, shared_out: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, shared_gate: Optional[torch.Tensor] = None) -> None:
     """``out[t] = sum_j weights[t, j] * y[place[t, j]] (+ shared_out[t])``, summed in 32-bit in the order of ``j``;
-    ``place`` None: the rows of ``y`` stand in the order of the pairs."""
-    _cuda(y, place, weights, shared_out, out)
+    ``place`` None: the rows of ``y`` stand in the order of the pairs.  ``shared_gate`` float32 ``[T]``: the shared
+    expert's row of token ``t`` is multiplied by ``shared_gate[t]``."""
+    _cuda(y, place, weights, shared_out, out, shared_gate)
+    if shared_gate is not None and (shared_out is None or shared_gate.dtype != torch.float32 or shared_gate.numel() != weights.shape[0]):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_combine: shared_gate float32 [T] goes with shared_out")
     T, top = weights.shape
     H = y.shape[1]
     if y.stride(1) != 1 or out.shape != (T, H) or not out.is_contiguous() \
             or (shared_out is not None and (shared_out.shape != (T, H) or not shared_out.is_contiguous()
                                             or shared_out.dtype != out.dtype)):
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "moe_combine: y [n, H], out and shared_out contiguous [T, H]")
-    f = _fn("moe", "photon_moe_combine",
-            [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(y), y.stride(0), _dtype_code(y), _ptr(place), _ptr(weights), top, _ptr(shared_out), _ptr(out),
-             _dtype_code(out), T, H, _stream()), "moe_combine")
+    f = _fn("moe", "photon_moe_combine_ex",
+            [c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), y.stride(0), _dtype_code(y), _ptr(place), _ptr(weights), top, _ptr(shared_out), _ptr(shared_gate),
+             _ptr(out), _dtype_code(out), T, H, _stream()), "moe_combine")
 
 
 def moe_gather(x: torch.Tensor, srt: torch.Tensor, div: int) -> torch.Tensor:
@@ -1118,10 +1275,11 @@ def moe_gemv_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def moe_gemv(x: torch.Tensor, x_div: int, ids: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, glu: bool = False,
-             activation: str = "silu") -> None:
+             activation: Optional[str] = None) -> None:
     """A decode step's few (token, choice) pairs: ``out[p] = weight[ids[p]] @ x[p // x_div]``, one matrix-vector
     product per pair in the order of the pairs, the expert's rows streamed once.  bfloat16 in, bfloat16 or float32 out."""
     _cuda(x, ids, weight, out)
+    act = ACTIVATIONS[activation or "silu"] if glu or activation else ACT_NONE
     E, N, K = weight.shape
     n = ids.numel()
     if not moe_gemv_supported(x, weight) or x.shape[1] != K:
@@ -1131,7 +1289,7 @@ def moe_gemv(x: torch.Tensor, x_div: int, ids: torch.Tensor, weight: torch.Tenso
     f = _fn("moe", "photon_moe_gemv",
             [c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), x.stride(0), int(x_div), _ptr(ids), n, _ptr(weight), _ptr(out), out.stride(0), _dtype_code(out), N, K,
-             int(glu), ACTIVATIONS[activation], _stream()), "moe_gemv")
+             int(glu), act, _stream()), "moe_gemv")
 
 
 # ----------------------------------------------------------------------------- sampling

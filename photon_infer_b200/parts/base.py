@@ -56,15 +56,32 @@ class PagedCacheSpec:
     visible; an integer: only the last ``window`` keys do, and pages behind the
     window are given back.  Layers with equal specs share one group of pages.
     ``values`` False: one row of ``n_kv_heads * head_dim`` per token and no value rows (a
-    mixer that caches a latent from which it derives keys and values alike)."""
+    mixer that caches a latent from which it derives keys and values alike).
+    ``value_dim``: width of a value where it differs from a key's (None: ``head_dim``); keys and
+    values then live in two tensors.  ``keep_first``: with a window, the first ``keep_first`` tokens
+    of a request stay visible for good, so the pages that hold them are not given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def planes(self) -> int:
         return 2 if self.values else 1
+
+    @property
+    def split_planes(self) -> bool:
+        """Keys and values of different widths: one tensor each instead of two planes of one."""
+        return self.values and self.value_dim is not None and self.value_dim != self.head_dim
+
+    @property
+    def row_width(self) -> int:
+        """Numbers cached per token and key/value head."""
+        if not self.values:
+            return self.head_dim
+        return self.head_dim + (self.value_dim if self.value_dim is not None else self.head_dim)
 
 
 @dataclasses.dataclass(frozen=True)

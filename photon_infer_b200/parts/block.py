@@ -17,11 +17,16 @@ from .registry import register_block
 
 
 class PreNormBlock(Block):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, feed_forward: Optional[FeedForward] = None):
+        if (norm2 is None) != (feed_forward is None):
+            raise ValueError("a pre-norm block has a second norm exactly when it has a feed-forward")
         self.norm1, self._mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
     def parts(self) -> Dict[str, Part]:
-        return {"norm1": self.norm1, "mixer": self._mixer, "norm2": self.norm2, "feed_forward": self.feed_forward}
+        p = {"norm1": self.norm1, "mixer": self._mixer}
+        if self.feed_forward is not None:
+            p.update(norm2=self.norm2, feed_forward=self.feed_forward)
+        return p
 
     def mixer(self) -> Mixer:
         return self._mixer
@@ -37,6 +42,8 @@ class PreNormBlock(Block):
         else:
             h = self.norm1.add_forward(delta, residual, ctx.dtype)
             a = self._mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return residual, a                      # a layer without a feed-forward: the mixer's output stays pending
         if self.feed_forward.fuses_norm(self.norm2, residual, ctx):
             d, residual = self.feed_forward.forward_with_norm(residual, a, self.norm2, ctx)
         else:

@@ -12,6 +12,13 @@ choices and adds the shared expert's output.  That is the float32 path and the o
 rows.  A bfloat16 decode step (a handful of pairs) skips the sort and runs one matrix-vector product per pair;
 a bfloat16 step with many rows hands the sorted rows to the library's grouped product.  The experts' matrices are stacked into ``[E, 2 ff, H]`` and
 ``[E, H, ff]`` when loaded.
+
+Variants, all by parameter.  ``gated`` False: an expert is ``W_down act(W_up h)`` (tensors ``e<i>.up``, ``e<i>.down``;
+the stack is ``[E, ff, H]``), and so is the shared expert.  ``router_bias`` False: no ``router.b``.  ``scoring``
+``softmax_all``: scores are the softmax over all experts, the experts form ``groups`` equal groups of neighbours of
+which only the ``keep_groups`` with the largest best score may be chosen from, and the weights are the chosen scores
+over their sum times ``route_scale``.  ``shared_gate``: the shared expert's output is multiplied by
+``sigmoid(W_sg h)``, one number per token (``shared.sg [1, H]``), computed with the router's logits in 32-bit.
 """
 from __future__ import annotations
 
@@ -32,7 +39,9 @@ class MoEFeedForward(FeedForward):
         return list(self.kernel_modules) + (["gemm_skinny", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, shared_size: Optional[int] = None,
-                 activation: str = "silu", shared_activation: Optional[str] = None):
+                 activation: str = "silu", shared_activation: Optional[str] = None, gated: bool = True,
+                 router_bias: bool = True, scoring: str = "softmax_chosen", groups: int = 1, keep_groups: Optional[int] = None,
+                 route_scale: float = 1.0, shared_gate: bool = False):
         if not 1 <= top <= experts:
             raise ValueError("a token uses between one and all of the experts")
         if activation not in ops.ACTIVATIONS:
@@ -41,65 +50,95 @@ class MoEFeedForward(FeedForward):
         self.expert_size, self.shared_size = expert_size, shared_size
         self.activation = activation
         self.shared_activation = shared_activation or activation
+        if scoring not in ops.ROUTER_SCORING:
+            raise ValueError(f"unknown router scoring {scoring!r}")
+        self.gated, self.router_bias, self.scoring = bool(gated), bool(router_bias), scoring
+        self.groups = int(groups or 1)
+        self.keep_groups = int(keep_groups) if keep_groups else self.groups
+        if experts % self.groups or not 1 <= self.keep_groups <= self.groups or self.keep_groups * (experts // self.groups) < top:
+            raise ValueError("the experts must split into equal groups, and the kept groups must hold at least `top` experts")
+        self.route_scale = float(route_scale)
+        self.shared_gate = bool(shared_gate) and bool(shared_size)
+        self.w_shared_gate = None
         self.w_router = self.b_router = self.w_gate_up = self.w_down = None
         self.shared_gate_up = self.shared_down = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         H, F = self.hidden_size, self.expert_size
-        specs = [TensorSpec("router", (self.experts, H)), TensorSpec("router.b", (self.experts,), role="vector", init="normal")]
+        specs = [TensorSpec("router", (self.experts, H))]
+        if self.router_bias:
+            specs.append(TensorSpec("router.b", (self.experts,), role="vector", init="normal"))
         for e in range(self.experts):
-            specs += [TensorSpec(f"e{e}.gate", (F, H)), TensorSpec(f"e{e}.up", (F, H)), TensorSpec(f"e{e}.down", (H, F))]
+            specs += ([TensorSpec(f"e{e}.gate", (F, H))] if self.gated else []) + \
+                     [TensorSpec(f"e{e}.up", (F, H)), TensorSpec(f"e{e}.down", (H, F))]
         if self.shared_size:
             S = self.shared_size
-            specs += [TensorSpec("shared.gate", (S, H)), TensorSpec("shared.up", (S, H)), TensorSpec("shared.down", (H, S))]
+            specs += ([TensorSpec("shared.gate", (S, H))] if self.gated else []) + \
+                     [TensorSpec("shared.up", (S, H)), TensorSpec("shared.down", (H, S))]
+            if self.shared_gate:
+                specs.append(TensorSpec("shared.sg", (1, H)))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         E = self.experts
         self.w_router = tensors["router"].contiguous()
-        self.b_router = tensors["router.b"].contiguous()
-        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0) for e in range(E)]).contiguous()
+        self.b_router = tensors["router.b"].contiguous() if self.router_bias else None
+        # the first matrix of every expert: [gate rows; up rows] of a gated expert, the up rows of a plain one
+        first = (lambda p: torch.cat([tensors[p + "gate"], tensors[p + "up"]], dim=0)) if self.gated else (lambda p: tensors[p + "up"])
+        self.w_gate_up = torch.stack([first(f"e{e}.") for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         if self.shared_size:
-            self.shared_gate_up = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            self.shared_gate_up = first("shared.").contiguous()
             self.shared_down = tensors["shared.down"].contiguous()
+            if self.shared_gate:
+                self.w_shared_gate = tensors["shared.sg"].contiguous()
 
     def weight_bytes(self) -> int:
         """What a step reads at most: the router, the shared expert and every expert once."""
         ws = [self.w_router, self.w_gate_up, self.w_down] + ([self.shared_gate_up, self.shared_down] if self.shared_size else [])
         return sum(w.numel() * w.element_size() for w in ws)
 
+    def _shared(self, h: torch.Tensor) -> torch.Tensor:
+        if self.gated:
+            return project(ops.linear_swiglu(h, self.shared_gate_up, self.shared_activation), self.shared_down)
+        return project(ops.activation(project(h, self.shared_gate_up), self.shared_activation), self.shared_down)
+
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = h.shape
         n = T * self.top
-        ids, weights, counts = ops.moe_route(h, self.w_router, self.b_router, self.top)
-        shared = None
-        if self.shared_size:
-            shared = project(ops.linear_swiglu(h, self.shared_gate_up, self.shared_activation), self.shared_down)
+        routed = ops.moe_route(h, self.w_router, self.b_router, self.top, self.scoring, self.groups, self.keep_groups,
+                               self.route_scale, self.w_shared_gate)
+        ids, weights, counts = routed[:3]
+        sgate = routed[3] if self.w_shared_gate is not None else None
+        shared = self._shared(h) if self.shared_size else None
+        glu, act_name = self.gated, self.activation
         out = torch.empty((T, H), dtype=h.dtype, device=h.device)
         if n <= GEMV_MAX_PAIRS and ops.moe_gemv_supported(h, self.w_gate_up) and self.expert_size % 8 == 0:
             # a decode step: nothing is sorted, every pair streams its expert's matrices once
             act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
-            ops.moe_gemv(h, self.top, ids, self.w_gate_up, act, glu=True, activation=self.activation)
+            ops.moe_gemv(h, self.top, ids, self.w_gate_up, act, glu=glu, activation=act_name)
             y = torch.empty((n, H), dtype=torch.float32, device=h.device)
             ops.moe_gemv(act, 1, ids, self.w_down, y)
-            ops.moe_combine(y, None, weights, shared, out)
+            ops.moe_combine(y, None, weights, shared, out, sgate)
             return out
         offsets, srt, place, tiles, num_tiles, max_tiles = ops.moe_align(ids, counts)
         if h.dtype == torch.bfloat16 and n >= GROUPED_LIBRARY_PAIRS and H % 8 == 0 and self.expert_size % 8 == 0:
             # many bfloat16 rows: the library's grouped product over the rows gathered in sorted order
             xs = ops.moe_gather(h, srt, self.top)
             gate_up = torch._grouped_mm(xs, self.w_gate_up.transpose(1, 2), offs=offsets[1:])
-            act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
-            ops.swiglu(gate_up, act, self.activation)
+            if glu:
+                act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
+                ops.swiglu(gate_up, act, act_name)
+            else:
+                act = ops.activation(gate_up, act_name)
             y = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=offsets[1:])
-            ops.moe_combine(y, place, weights, shared, out)
+            ops.moe_combine(y, place, weights, shared, out, sgate)
             return out
         act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
-        ops.moe_gemm(h, srt, self.top, self.w_gate_up, act, tiles, num_tiles, max_tiles, glu=True, activation=self.activation)
+        ops.moe_gemm(h, srt, self.top, self.w_gate_up, act, tiles, num_tiles, max_tiles, glu=glu, activation=act_name)
         y = torch.empty((n, H), dtype=torch.float32, device=h.device)
         ops.moe_gemm(act, None, 1, self.w_down, y, tiles, num_tiles, max_tiles)
-        ops.moe_combine(y, place, weights, shared, out)
+        ops.moe_combine(y, place, weights, shared, out, sgate)
         return out
 
 

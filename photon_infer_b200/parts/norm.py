@@ -1,4 +1,4 @@
-"""RMSNorm: ``y = w * (x / sqrt(mean(x^2) + eps))`` in 32-bit
+"""Norms of the residual stream.  RMSNorm: ``y = w * (x / sqrt(mean(x^2) + eps))`` in 32-bit
 (include/photon/ops/kernels/rmsnorm_kernel.hpp:71-86), fused with the residual sum
 that precedes it (the reference runs a separate add kernel,
 src/arch/transformer_block.cpp:270,295)."""
@@ -47,4 +47,46 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """``y = (x - mean(x)) / sqrt(var(x) + eps) * w + b`` in 32-bit, the variance being the mean of the squared
+    deviations; fused with the residual sum before it like ``RMSNorm``.  ``bias_name`` None: no bias."""
+    kernel_modules = ("elementwise",)
+
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", bias_name: Optional[str] = "bias"):
+        self.size = size
+        self.eps = float(eps)
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [TensorSpec(self.weight_name, (self.size,), role="vector", init="norm")]
+        if self.bias_name is not None:
+            specs.append(TensorSpec(self.bias_name, (self.size,), role="vector", init="normal"))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name]
+        self.bias = tensors[self.bias_name] if self.bias_name is not None else None
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.weight, self.bias) if t is not None)
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return self.add_forward(None, x, out_dtype)
+
+    def add_forward(self, delta, residual, out_dtype):
+        out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+        d1, d2 = delta_pair(delta)
+        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, delta2=d2)
+        return out
+
+    def add_forward_rows(self, delta, residual, rows, out_dtype):
+        out = torch.empty((rows.numel(), residual.shape[1]), dtype=out_dtype, device=residual.device)
+        d1, d2 = delta_pair(delta)
+        ops.add_layernorm(d1, residual, self.weight, self.bias, self.eps, out, rows=rows, delta2=d2)
+        return out
+
+
 register_norm("rms_norm", RMSNorm)
+register_norm("layer_norm", LayerNorm)

@@ -48,4 +48,4 @@ def create_part(table_name: str, kind: str, params: dict):
 
 
 def _ensure_builtin() -> None:
-    from . import attention, block, gla, latent_attention, mlp, moe, norm, rope, stream  # noqa: F401  (each registers itself)
+    from . import attention, block, gla, latent_attention, mlp, moe, norm, normed_attention, rope, stream  # noqa: F401  (each registers itself)
