@@ -87,9 +87,20 @@ struct FlashParams {
                                           // KEYS kernel takes a request's positions as context_len - n .. context_len - 1
   float* part_acc; float* part_ml; int* tickets;   // scratch of the KEYS mode with splits
   int n_q, n_kv, group, page_size, page_shift, num_pages, window, num_splits, tiles_per_seq;   // page_shift: log2(page_size) or -1
-  float scale_log2;                       // scale * log2(e)
+  float scale_log2;                       // scale * log2(e); with bounded scores log2(e) alone
   int* err;
+  // Three more rules (all off at 0).  keep_first: with a window, keys 0 .. keep_first - 1 stay visible behind it.
+  // sink: the softmax has one more key with score 0 and no value.  softcap: scores become
+  // softcap * tanh(score * scale / softcap); cap_in = scale / softcap.
+  int keep_first, sink;
+  float softcap, cap_in;
 };
+
+// tanh through one exponential and one reciprocal: 1 - 2 / (2^(2 x log2 e) + 1); absolute error about 1e-7.
+__device__ __forceinline__ float fa_tanh(float x) {
+  const float e = fast_exp2(x * 2.8853900817779268f);
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
 
 // Copies the keys [key0, key0 + 64) of key/value head g into one stage (K tile, then V tile).
 // Rows outside [lo, hi] or without a page are filled with zeros.
@@ -97,11 +108,12 @@ struct FlashParams {
 __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* table, const int* table_s, int g,
                                              int key0, int lo, int hi, bf16* ks, bf16* vs, int t_for_err,
                                              int tid, int nthreads) {
+  const int kept = P.keep_first;
   constexpr int CPR = HEAD_DIM / 8;                       // 16-byte chunks per row
   for (int c = tid; c < FA_TILE_K * CPR; c += nthreads) {
     const int r = c / CPR, cc = c - r * CPR;
     const int key = key0 + r;
-    bool valid = key >= lo && key <= hi;
+    bool valid = (key >= lo || key < kept) && key <= hi;
     size_t src = 0;
     if (valid) {
       const int pidx = P.page_shift >= 0 ? (key >> P.page_shift) : key / P.page_size;
@@ -127,7 +139,8 @@ __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* ta
 template <int NT, bool MASK>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const bf16* ks, const bf16* vs, int krow,
                                           int key_base, int pos0, int pos1, int lo0, int lo1, float scale_log2,
-                                          float (&m)[2], float (&l)[2], float (&o)[FA_ND][4]) {
+                                          float (&m)[2], float (&l)[2], float (&o)[FA_ND][4], int kept = 0,
+                                          float softcap = 0.f, float cap_in = 0.f) {
   const int lane = threadIdx.x & 31;
   float s[NT][4];
 #pragma unroll
@@ -145,6 +158,14 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
       mma_bf16(s[j + 1], qa[kd], b[2], b[3]);
     }
   }
+  if (softcap > 0.f) {
+    // bounded scores; scale_log2 is log2(e) alone then
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) s[j][u] = softcap * fa_tanh(s[j][u] * cap_in);
+    }
+  }
   // scale, mask, running softmax (base 2); the scale is applied inside the exponent: 2^(s*c - m*c)
   const int c2 = (lane & 3) * 2;
   float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -152,10 +173,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
   for (int j = 0; j < NT; ++j) {
     if (MASK) {
       const int key = key_base + krow + j * 8 + c2;
-      s[j][0] = (key >= lo0 && key <= pos0) ? s[j][0] : -INFINITY;
-      s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? s[j][1] : -INFINITY;
-      s[j][2] = (key >= lo1 && key <= pos1) ? s[j][2] : -INFINITY;
-      s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? s[j][3] : -INFINITY;
+      s[j][0] = ((key >= lo0 || key < kept) && key <= pos0) ? s[j][0] : -INFINITY;
+      s[j][1] = ((key + 1 >= lo0 || key + 1 < kept) && key + 1 <= pos0) ? s[j][1] : -INFINITY;
+      s[j][2] = ((key >= lo1 || key < kept) && key <= pos1) ? s[j][2] : -INFINITY;
+      s[j][3] = ((key + 1 >= lo1 || key + 1 < kept) && key + 1 <= pos1) ? s[j][3] : -INFINITY;
     }
     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
     mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
@@ -252,7 +273,12 @@ flash_attention_kernel(const FlashParams P) {
   const int pos_first = by_len ? ctx_len - ntok + tfirst : P.positions[tok0 + tfirst];
   const int pos_last = by_len ? ctx_len - ntok + tlast : P.positions[tok0 + tlast];
   const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
-  int tile_begin = key_lo / FA_TILE_K, tile_end = pos_last / FA_TILE_K + 1;     // key tiles [begin, end)
+  // Key tiles: with kept first keys, the tiles that hold them and lie below the window's first tile come first.
+  // The walk counts through both stretches (tile_begin .. tile_end are counters, tile_of gives the key tile).
+  const int win_tile = key_lo / FA_TILE_K;
+  const int kept_tiles = (P.keep_first > 0 && key_lo > 0) ? min((P.keep_first + FA_TILE_K - 1) / FA_TILE_K, win_tile) : 0;
+  auto tile_of = [&](int c) { return c < kept_tiles ? c : win_tile + c - kept_tiles; };
+  int tile_begin = 0, tile_end = kept_tiles + pos_last / FA_TILE_K + 1 - win_tile;
   if (KEYS_MODE && P.num_splits > 1) {
     const int per = (tile_end - tile_begin + P.num_splits - 1) / P.num_splits;
     tile_begin += split * per;
@@ -286,7 +312,7 @@ flash_attention_kernel(const FlashParams P) {
   // prologue: the first STAGES - 1 tiles (the Q copy joins the first group)
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (i < ntiles) load_kv_tile(P, table, tsm, g, (tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0, stid, sthreads);
+    if (i < ntiles) load_kv_tile(P, table, tsm, g, tile_of(tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0, stid, sthreads);
     cp_async_commit();
   }
 
@@ -324,7 +350,7 @@ flash_attention_kernel(const FlashParams P) {
     {
       const int nx = i + STAGES - 1;
       if (nx < ntiles)
-        load_kv_tile(P, table, tsm, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % STAGES),
+        load_kv_tile(P, table, tsm, g, tile_of(tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % STAGES),
                      stage_v(nx % STAGES), tok0, stid, sthreads);
       cp_async_commit();
     }
@@ -336,26 +362,26 @@ flash_attention_kernel(const FlashParams P) {
         ldsm4(qa[kd], qs + (wrow + (lane & 15)) * FA_LD + kd * 16 + ((lane >> 4) << 3));
     }
     const int st = i % STAGES;
-    const int key_base = (tile_begin + i) * FA_TILE_K;
+    const int key_base = tile_of(tile_begin + i) * FA_TILE_K;
     if (KEYS_MODE) {
       // every warp takes 16 keys of the tile
       const int k0 = key_base + wq * 16;
       if (k0 <= warp_pos_max) {
         if (k0 + 15 <= warp_pos_min && k0 >= warp_lo_max)
           warp_tile<2, false>(qa, stage_k(st), stage_v(st), wq * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                              P.scale_log2, m, l, o);
+                              P.scale_log2, m, l, o, P.keep_first, P.softcap, P.cap_in);
         else
           warp_tile<2, true>(qa, stage_k(st), stage_v(st), wq * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                             P.scale_log2, m, l, o);
+                             P.scale_log2, m, l, o, P.keep_first, P.softcap, P.cap_in);
       }
     } else {
       if (key_base <= warp_pos_max) {                                      // tiles after the warp's last row are skipped
         if (key_base + FA_TILE_K - 1 <= warp_pos_min && key_base >= warp_lo_max)
           warp_tile<8, false>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                              P.scale_log2, m, l, o);
+                              P.scale_log2, m, l, o, P.keep_first, P.softcap, P.cap_in);
         else
           warp_tile<8, true>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                             P.scale_log2, m, l, o);
+                             P.scale_log2, m, l, o, P.keep_first, P.softcap, P.cap_in);
       }
     }
     group_sync();                                                          // the stage may be overwritten
@@ -376,6 +402,7 @@ flash_attention_kernel(const FlashParams P) {
       const int row = row0 + wrow + (lane >> 2) + h2 * 8;
       if (row >= rows) continue;
       const int tk = row / G, h = row - tk * G;
+      if (P.sink) l[h2] += exp2f(-m[h2]);                                   // the sink's weight, relative to the running maximum
       const float inv = l[h2] > 0.f ? 1.f / l[h2] : 0.f;
       bf16* dst = P.out + (size_t)(tok0 + tk) * P.out_stride + (size_t)(g * G + h) * HEAD_DIM + (lane & 3) * 2;
 #pragma unroll
@@ -421,6 +448,7 @@ flash_attention_kernel(const FlashParams P) {
     const int tk = r / G, h = r - tk * G;
     const int head = g * G + h;
     if (P.num_splits == 1) {
+      if (P.sink && M != -INFINITY) L += exp2f(-M);
       P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
     } else {
       const size_t slot = ((size_t)(tok0 + tk) * n_q + head) * P.num_splits + split;
@@ -452,6 +480,7 @@ flash_attention_kernel(const FlashParams P) {
         L += __ldcg(P.part_ml + (base + s2) * 2 + 1) * sc;
         A += __ldcg(P.part_acc + (base + s2) * HEAD_DIM + d) * sc;
       }
+      if (P.sink) L += exp2f(-M);
     }
     P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
   }
@@ -479,7 +508,23 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
                                       int* tickets, int S, int max_tokens_per_seq, int n_q, int n_kv, int d,
                                       int page_size, int num_pages, int window, float scale, int num_splits,
                                       int nsub, int mode, int* err, cudaStream_t stream) {
+  return photon_flash_attention_ex(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, cu_tokens, positions,
+                                   context_lens, part_acc, part_ml, tickets, S, max_tokens_per_seq, n_q, n_kv, d, page_size,
+                                   num_pages, window, scale, num_splits, nsub, mode, err, 0, 0, 0.f, stream);
+}
+
+// The same with kept first keys (with a window, keys 0 .. keep_first - 1 stay visible behind it), a sink (one more
+// key with score 0 and no value in the softmax) and bounded scores (softcap * tanh(score * scale / softcap); 0: off).
+PHOTON_API int photon_flash_attention_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                                         const void* v_cache, const int* block_table, int max_pages,
+                                         const int* cu_tokens, const int* positions, const int* context_lens,
+                                         float* part_acc, float* part_ml,
+                                         int* tickets, int S, int max_tokens_per_seq, int n_q, int n_kv, int d,
+                                         int page_size, int num_pages, int window, float scale, int num_splits,
+                                         int nsub, int mode, int* err, int keep_first, int sink, float softcap,
+                                         cudaStream_t stream) {
   if (S <= 0) return 0;
+  if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
   if (((uintptr_t)q % 16) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
     return PHOTON_ERR_ARGUMENT;
@@ -495,6 +540,8 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   P.page_shift = -1;
   for (int sh = 0; sh < 20; ++sh) if ((1 << sh) == page_size) P.page_shift = sh;
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
+  P.keep_first = window > 0 ? keep_first : 0; P.sink = sink; P.softcap = softcap; P.cap_in = 0.f;
+  if (softcap > 0.f) { P.cap_in = scale / softcap; P.scale_log2 = 1.4426950408889634f; }
   const size_t ring = (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD;
   const size_t ring2 = (size_t)2 * 2 * FA_TILE_K * FA_LD;                   // two stages
   const size_t smem_rows = ((size_t)FA_ROWS * FA_LD + ring) * sizeof(bf16);

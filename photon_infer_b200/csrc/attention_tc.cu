@@ -79,8 +79,12 @@ struct AttnTcParams {
   const int* cu_tokens;                            // [S + 1]
   const int* positions;                            // [T]
   int n_kv, group, tile_rows, page_size, num_pages, box_rows, window, tiles_per_seq, total_rows;
-  float scale_log2;
+  float scale_log2;                                // scale * log2(e); with bounded scores log2(e) alone
   int* err;
+  // keep_first: with a window, keys 0 .. keep_first - 1 stay visible behind it.  sink: one more key with score 0 and no
+  // value in the softmax.  softcap > 0: scores become softcap * tanh(score * cap_in), cap_in = scale / softcap.
+  int keep_first, sink;
+  float softcap, cap_in;
 };
 
 // D += A B with A in tensor memory (128 lanes x 8 columns of packed bfloat16 pairs per 16 of K), B in shared memory.
@@ -131,8 +135,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int t_first = row0 / G, t_last = (row0 + nrows - 1) / G;
   const int pos_first = P.positions[tok0 + t_first], pos_last = P.positions[tok0 + t_last];
   const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
+  // Key tiles: with kept first keys, the tiles that hold them and lie below the window's first tile come first;
+  // i counts through both stretches and tile_of gives the key tile.
   const int tile_begin = key_lo / AT_KT;
-  const int ntiles = pos_last / AT_KT + 1 - tile_begin;
+  const int kept_tiles = (P.keep_first > 0 && key_lo > 0) ? min((P.keep_first + AT_KT - 1) / AT_KT, tile_begin) : 0;
+  const int ntiles = kept_tiles + pos_last / AT_KT + 1 - tile_begin;
+  auto tile_of = [&](int i) { return i < kept_tiles ? i : tile_begin + i - kept_tiles; };
 
   extern __shared__ unsigned char at_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)at_dyn + 1023) & ~(uintptr_t)1023);
@@ -183,8 +191,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // the page of this lane's part, looked up before the wait for a free stage
       int rowc = P.total_rows;                      // outside the map: the part is filled with zeros
       if (lane < boxes) {
-        const int key = (tile_begin + i) * AT_KT + lane * P.box_rows;
-        if (key <= pos_last && key + P.box_rows - 1 >= key_lo) {
+        const int key = tile_of(i) * AT_KT + lane * P.box_rows;
+        if (key <= pos_last && (key + P.box_rows - 1 >= key_lo || key < P.keep_first)) {
           const int pidx = key / P.page_size, slot = key - pidx * P.page_size;
           const int page = table[pidx];
           if (page < 0 || page >= P.num_pages) report_error(P.err, PHOTON_DEV_BAD_PAGE, tok0, key, page);
@@ -267,6 +275,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const bool valid = r < P.tile_rows && row < rows;
     const int pos = valid ? P.positions[tok0 + row / G] : -1;
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+    const int kept = P.keep_first;
+    const float cap = P.softcap, cap_in = P.cap_in * 2.8853900817779268f;     // tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1)
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float c = P.scale_log2;
     float m_used = -INFINITY, l = 0.f;
@@ -279,7 +289,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int b = i % AT_NBUF;
       if (!wait_all(&s_full[b], (i / AT_NBUF) & 1)) { ok = false; break; }
       tc_fence_after();
-      const int key_base = (tile_begin + i) * AT_KT;
+      const int key_base = tile_of(i) * AT_KT;
       const bool masked = !(key_base + AT_KT - 1 <= pos && key_base >= lo);
       // 64 scores of this row: keys key_base + 64 * half ..; those the row may not see become -inf
       uint32_t sv[64];
@@ -287,11 +297,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc_ld32_issue(lane_addr + b * AT_KT + half * 64, sv);
         tc_ld32_issue(lane_addr + b * AT_KT + half * 64 + 32, sv + 32);
         tc_ld_wait();
+        if (cap > 0.f) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const float e = at_exp2(__uint_as_float(sv[j]) * cap_in);
+            sv[j] = __float_as_uint(cap - __fdividef(2.0f * cap, e + 1.0f));
+          }
+        }
         if (masked) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) {
             const int key = key_base + half * 64 + j;
-            sv[j] = (key >= lo && key <= pos) ? sv[j] : 0xff800000u;       // -inf
+            sv[j] = ((key >= lo || key < kept) && key <= pos) ? sv[j] : 0xff800000u;       // -inf
           }
         }
       };
@@ -381,6 +398,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     if (ok && ntiles > 0 && wait_all(&pv_done[(ntiles - 1) % AT_NBUF], ((ntiles - 1) / AT_NBUF) & 1)) {
       tc_fence_after();
+      if (P.sink && valid) l += exp2f(-m_used);     // the sink's weight, relative to the maximum in use
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int tk = valid ? row / G : 0, h = valid ? row - tk * G : 0;
       bf16* dst = P.out + (size_t)(tok0 + tk) * P.out_stride + (size_t)(g * G + h) * HEAD_DIM;
@@ -423,7 +441,19 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
                                    const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
                                    int page_size, int num_pages, int window, float scale, int* err,
                                    cudaStream_t stream) {
+  return photon_attention_tc_ex(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, cu_tokens, positions,
+                                S, max_tokens_per_seq, T, n_q, n_kv, d, page_size, num_pages, window, scale, err, 0, 0, 0.f,
+                                stream);
+}
+
+// The same with kept first keys, a sink and bounded scores (see AttnTcParams).
+PHOTON_API int photon_attention_tc_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                                      const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
+                                      const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
+                                      int page_size, int num_pages, int window, float scale, int* err, int keep_first,
+                                      int sink, float softcap, cudaStream_t stream) {
   if (S <= 0 || T <= 0) return 0;
+  if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
   const int G = n_q / n_kv;
   if (G > AT_ROWS) return PHOTON_ERR_UNSUPPORTED;
@@ -457,6 +487,8 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
   P.page_size = page_size;
   P.num_pages = num_pages; P.box_rows = box_rows; P.window = window; P.total_rows = (int)total_rows;
   P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
+  P.keep_first = window > 0 ? keep_first : 0; P.sink = sink; P.softcap = softcap; P.cap_in = 0.f;
+  if (softcap > 0.f) { P.cap_in = scale / softcap; P.scale_log2 = 1.4426950408889634f; }
   const long rows = (long)max_tokens_per_seq * G;
   P.tiles_per_seq = (int)((rows + P.tile_rows - 1) / P.tile_rows);
   if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;

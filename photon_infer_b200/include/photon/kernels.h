@@ -225,6 +225,14 @@ PHOTON_EXPORT int photon_flash_attention(const void* q, long q_stride, void* out
                            const int* positions, const int* context_lens, float* part_acc, float* part_ml, int* tickets,
                            int S, int max_tokens_per_seq, int n_q, int n_kv, int d, int page_size, int num_pages,
                            int window, float scale, int num_splits, int nsub, int mode, int* err, cudaStream_t stream);
+/* The same with kept first keys (with a window, keys < keep_first stay visible), a sink (one more key with score 0 and no
+ * value) and bounded scores (softcap * tanh(score * scale / softcap); 0: off). */
+PHOTON_EXPORT int photon_flash_attention_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
+                              const int* positions, const int* context_lens, float* part_acc, float* part_ml, int* tickets,
+                              int S, int max_tokens_per_seq, int n_q, int n_kv, int d, int page_size, int num_pages,
+                              int window, float scale, int num_splits, int nsub, int mode, int* err, int keep_first,
+                              int sink, float softcap, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_tc.cu (-DHEAD_DIM=64|128; bfloat16; tcgen05) */
 PHOTON_EXPORT int photon_attention_tc_head_dim(void);
@@ -233,6 +241,11 @@ PHOTON_EXPORT int photon_attention_tc(const void* q, long q_stride, void* out, l
                         const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
                         const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
                         int page_size, int num_pages, int window, float scale, int* err, cudaStream_t stream);
+PHOTON_EXPORT int photon_attention_tc_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                           const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
+                           const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
+                           int page_size, int num_pages, int window, float scale, int* err, int keep_first, int sink,
+                           float softcap, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_decode.cu (-DHEAD_DIM=64|128; bfloat16; TMA) */
 PHOTON_EXPORT int photon_attention_decode_head_dim(void);

@@ -449,7 +449,8 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
                     window: Optional[int], scale: float, num_splits: int, scratch: Optional[torch.Tensor],
                     rows_mode: bool, keys_mode: bool, err: Optional[torch.Tensor],
-                    context_lens: Optional[torch.Tensor] = None, key_groups: int = 1) -> None:
+                    context_lens: Optional[torch.Tensor] = None, key_groups: int = 1, keep_first: int = 0,
+                    sink: bool = False, softcap: Optional[float] = None) -> None:
     """Paged causal attention on the tensor cores.  ``cu_tokens [S + 1]`` gives each request's
     tokens in the step.  ``rows_mode``: run requests with more than 16 rows (tokens x heads per
     group); ``keys_mode``: run the others, their keys split over ``num_splits`` blocks.
@@ -458,7 +459,8 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     derives positions from it (a request's tokens of the step are its last ones) and saves a round trip.
     ``key_groups``: 1, 2 or 4 groups of four warps per block of the split-key kernel, each walking its own
     share of the block's keys (``flash_attention_max_groups`` bounds it); their results are merged in shared
-    memory, which is far cheaper than the merge of ``num_splits`` blocks through global memory."""
+    memory, which is far cheaper than the merge of ``num_splits`` blocks through global memory.
+    ``keep_first``, ``sink``, ``softcap``: as in ``paged_attention``."""
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, scratch, err, context_lens)
     if context_lens is not None:
         _int32(context_lens, "context_lens")
@@ -487,17 +489,17 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         if tickets.numel() < num_seqs * n_kv:
             raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "flash_attention: too many requests for the ticket buffer")
     mode = (1 if rows_mode else 0) | (2 if keys_mode else 0)
-    f = _fn("attention_flash", "photon_flash_attention",
+    f = _fn("attention_flash", "photon_flash_attention_ex",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-             c_int, c_void_p, c_void_p],
+             c_int, c_void_p, c_int, c_int, c_float, c_void_p],
             defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
              block_table.shape[1], _ptr(cu_tokens), _ptr(positions), _ptr(context_lens), _ptr(part_acc), _ptr(part_ml),
              _ptr(tickets),
              int(num_seqs), int(max_tokens_per_seq), n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0],
              int(window) if window else 0, float(scale), splits, int(key_groups) if keys_mode else 1, mode, _ptr(err),
-             _stream()), "flash_attention")
+             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "flash_attention")
     if rows_mode and keys_mode:
         global _launch_count
         _launch_count += 1
@@ -621,10 +623,12 @@ def attention_tc_supported(dtype: torch.dtype, head_dim: int, group: int, page_s
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_table: torch.Tensor, cu_tokens: torch.Tensor, positions: torch.Tensor,
                  num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
-                 window: Optional[int], scale: float, err: Optional[torch.Tensor]) -> None:
+                 window: Optional[int], scale: float, err: Optional[torch.Tensor], keep_first: int = 0,
+                 sink: bool = False, softcap: Optional[float] = None) -> None:
     """Paged causal attention of the requests that bring more than 16 rows (tokens x heads per
     group) in this step, on the tcgen05 tensor cores; the rows of the other requests are left
-    untouched (``flash_attention`` with ``keys_mode`` takes them)."""
+    untouched (``flash_attention`` with ``keys_mode`` takes them).  ``keep_first``, ``sink``, ``softcap``: as in
+    ``paged_attention``."""
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, err)
     T = q.shape[0]
     if n_kv <= 0 or n_q % n_kv or not attention_tc_supported(q.dtype, head_dim, n_q // n_kv, k_cache.shape[2]):
@@ -640,14 +644,15 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
         _int32(t, name)
     if cu_tokens.numel() < num_seqs + 1 or block_table.shape[0] < num_seqs:
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention_tc: cu_tokens and block_table must cover every request")
-    f = _fn("attention_tc", "photon_attention_tc",
+    f = _fn("attention_tc", "photon_attention_tc_ex",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_float,
+             c_void_p],
             defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
              block_table.shape[1], _ptr(cu_tokens), _ptr(positions), int(num_seqs), int(max_tokens_per_seq), T,
              n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale),
-             _ptr(err), _stream()), "attention_tc")
+             _ptr(err), int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "attention_tc")
 
 
 # ----------------------------------------------------------------------------- matrix products

@@ -147,58 +147,71 @@ class PagedAttention(Mixer):
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with a head size the tensor-core kernel is compiled for: that kernel.  float32 and
         other sizes: the general kernel, whose sums depend only on a token's position."""
-        group = ctx.groups[cache.group]
-        gsize = self.n_q // self.n_kv
         if ops.flash_attention_supported(q.dtype, self.head_dim):
-            # tensor cores: requests with many rows walk their keys in one block per 128 rows, requests
-            # with few rows (decoded tokens) split their keys over blocks
-            T = q.shape[0]
-            few = [n * gsize <= 16 for n in ctx.host_query_lens]
-            keys_mode, rows_mode = any(few), not all(few)
-            splits, groups, scratch = 1, 1, None
-            keys = ctx.max_context_len if self.window is None else min(self.window + ctx.max_query_len, ctx.max_context_len)
-            # decoded tokens with long contexts: the persistent TMA kernel
-            plan = None
-            pairs = sum(few) * self.n_kv
-            if keys_mode and (keys >= DECODE_TMA_MIN_KEYS.get(self.head_dim, 1 << 30)
-                              or pairs * keys >= DECODE_TMA_MIN_WORK.get(self.head_dim, 1 << 60)) \
-                    and ops.attention_decode_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2], ctx.num_seqs):
-                plan = ops.attention_decode_plan(sum(few), self.n_kv, keys, self.head_dim, cache.k.shape[2])
-            decode_tma = plan is not None
-            if keys_mode and not decode_tma:
-                if self._max_groups is None:
-                    self._max_groups = ops.flash_attention_max_groups(self.head_dim)
-                splits, groups = choose_key_shares(sum(few) * self.n_kv, keys, self._max_groups, sms=ops.sm_count(q.device))
-                # the kernel indexes its partial results by the token's place in the step, so beside a long prompt
-                # portion every share costs T rows: no more shares than 64 MB of them
-                per_share = T * self.n_q * (self.head_dim + 2) * 4
-                splits = max(1, min(splits, (64 << 20) // per_share))
-                if splits > 1:
-                    scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
-            if rows_mode and ops.USE_ATTENTION_TC and \
-                    ops.attention_tc_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2]):
-                # prompt portions: tensor memory and TMA; the split-key kernel keeps the decoded tokens
-                ops.attention_tc(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
-                                 ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
-                                 self.scale, ctx.error_flag)
-                rows_mode = False
-            if decode_tma:
-                chunk, chunks, items = plan
-                # one scratch buffer per device, shared by the layers and steps (they run one after the other) and never
-                # freed: a captured decode step keeps its address
-                scratch = ops.attention_decode_scratch(q.device, chunks * self.n_kv * 16 * (self.head_dim + 2))
-                ops.attention_decode(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.context_lens,
-                                     ctx.num_seqs, self.n_q, self.n_kv, self.head_dim, self.window, self.scale, chunk,
-                                     scratch, chunks, items, ctx.error_flag)
-                keys_mode = False
-            if rows_mode or keys_mode:
-                ops.flash_attention(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
-                                    ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
-                                    self.scale, splits, scratch, rows_mode, keys_mode, ctx.error_flag,
-                                    ctx.context_lens, groups)
+            attend_tensor_cores(self, q, out, ctx, cache)
             return
+        group = ctx.groups[cache.group]
         ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
+
+
+def attend_tensor_cores(mixer, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache,
+                        keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None) -> None:
+    """The tensor-core attention kernels for one step of ``mixer`` (anything with ``n_q``, ``n_kv``, ``head_dim``,
+    ``window``, ``scale`` and a ``_max_groups`` slot): requests with many rows walk their keys in one block per 128
+    rows, requests with few rows (decoded tokens) split their keys over blocks.  ``keep_first``, ``sink``,
+    ``softcap``: the rules of ``ops.paged_attention``; the persistent kernel for long contexts has none of them."""
+    self = mixer
+    extras = dict(keep_first=keep_first, sink=sink, softcap=softcap)
+    plain = not (keep_first or sink or softcap)
+    group = ctx.groups[cache.group]
+    gsize = self.n_q // self.n_kv
+    # tensor cores: requests with many rows walk their keys in one block per 128 rows, requests
+    # with few rows (decoded tokens) split their keys over blocks
+    T = q.shape[0]
+    few = [n * gsize <= 16 for n in ctx.host_query_lens]
+    keys_mode, rows_mode = any(few), not all(few)
+    splits, groups, scratch = 1, 1, None
+    keys = ctx.max_context_len if self.window is None else min(self.window + keep_first + ctx.max_query_len, ctx.max_context_len)
+    # decoded tokens with long contexts: the persistent TMA kernel
+    plan = None
+    pairs = sum(few) * self.n_kv
+    if plain and keys_mode and (keys >= DECODE_TMA_MIN_KEYS.get(self.head_dim, 1 << 30)
+                      or pairs * keys >= DECODE_TMA_MIN_WORK.get(self.head_dim, 1 << 60)) \
+            and ops.attention_decode_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2], ctx.num_seqs):
+        plan = ops.attention_decode_plan(sum(few), self.n_kv, keys, self.head_dim, cache.k.shape[2])
+    decode_tma = plan is not None
+    if keys_mode and not decode_tma:
+        if self._max_groups is None:
+            self._max_groups = ops.flash_attention_max_groups(self.head_dim)
+        splits, groups = choose_key_shares(sum(few) * self.n_kv, keys, self._max_groups, sms=ops.sm_count(q.device))
+        # the kernel indexes its partial results by the token's place in the step, so beside a long prompt
+        # portion every share costs T rows: no more shares than 64 MB of them
+        per_share = T * self.n_q * (self.head_dim + 2) * 4
+        splits = max(1, min(splits, (64 << 20) // per_share))
+        if splits > 1:
+            scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
+    if rows_mode and ops.USE_ATTENTION_TC and \
+            ops.attention_tc_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2]):
+        # prompt portions: tensor memory and TMA; the split-key kernel keeps the decoded tokens
+        ops.attention_tc(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
+                         ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
+                         self.scale, ctx.error_flag, **extras)
+        rows_mode = False
+    if decode_tma:
+        chunk, chunks, items = plan
+        # one scratch buffer per device, shared by the layers and steps (they run one after the other) and never
+        # freed: a captured decode step keeps its address
+        scratch = ops.attention_decode_scratch(q.device, chunks * self.n_kv * 16 * (self.head_dim + 2))
+        ops.attention_decode(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.context_lens,
+                             ctx.num_seqs, self.n_q, self.n_kv, self.head_dim, self.window, self.scale, chunk,
+                             scratch, chunks, items, ctx.error_flag)
+        keys_mode = False
+    if rows_mode or keys_mode:
+        ops.flash_attention(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
+                            ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
+                            self.scale, splits, scratch, rows_mode, keys_mode, ctx.error_flag,
+                            ctx.context_lens, groups, **extras)
 
 
 #: Contexts (keys a decoded token may see) from which the persistent TMA kernel takes the decoded tokens, by head

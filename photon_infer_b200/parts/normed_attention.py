@@ -20,6 +20,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
+from .attention import attend_tensor_cores
 from .base import LayerCache, Mixer, PagedCacheSpec, StepContext, TensorSpec
 from .linear import project
 from .registry import register_mixer
@@ -54,6 +55,7 @@ class NormedAttention(Mixer):
         self.w_o: Optional[torch.Tensor] = None
         self.q_norm = self.k_norm = None
         self.inv_freq: Optional[torch.Tensor] = None
+        self._max_groups: Optional[int] = None          # groups of warps per block of the split-key kernel, asked once
 
     # -- sizes of the sections of the fused row
     @property
@@ -126,8 +128,13 @@ class NormedAttention(Mixer):
         return project(attn, self.w_o)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        """float32, and sizes the tensor-core kernels are not compiled for: the general kernel, whose sums depend on a
-        token's position alone.  bfloat16 decode steps share a token's keys out over blocks."""
+        """bfloat16 with heads the tensor-core kernels are compiled for (keys and values of one width): those
+        kernels, tcgen05 for prompt portions and the split-key kernel for decoded tokens.  float32 and other sizes:
+        the general kernel, whose sums depend on a token's position alone; its bfloat16 decode steps share a
+        token's keys out over blocks."""
+        if self._flash_ok(q.dtype):
+            attend_tensor_cores(self, q, out, ctx, cache, keep_first=self.keep_first, sink=self.sink, softcap=self.softcap)
+            return
         group = ctx.groups[cache.group]
         splits = 1
         if q.dtype == torch.bfloat16 and ctx.max_query_len == 1:

@@ -208,3 +208,106 @@ def finelix_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
     if key not in _finelix_cache:
         _finelix_cache[key] = PlainFinelix.from_folder(folder).logits(ids)
     return _finelix_cache[key]
+
+
+# ----------------------------------------------------------------------------- Fekopel
+
+def _att(heads, kv_heads, dim, vdim, scale, size=None):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale)
+    if size:
+        m["mask"] = dict(size=size)
+    return m
+
+
+def _att2(heads, kv_heads, dim, vdim, scale, size=None, keep_first=None, rot=None, softcap=None):
+    m = _att(heads, kv_heads, dim, vdim, scale, size)
+    if keep_first is not None:
+        m["mask"]["keep_first"] = keep_first
+    if rot:
+        m["rot"] = dict(base=rot[0], dims=rot[1])
+    if softcap:
+        m["softcap"] = softcap
+    return m
+
+
+def _fmoe(experts, top, ff, shared=None, groups=None, scale=1.0):
+    r = dict(experts=experts, top=top, scale=scale)
+    if groups:
+        r["groups"] = dict(count=groups[0], keep=groups[1])
+    m = dict(kind="moe", router=r, expert=dict(ff=ff))
+    if shared:
+        m["shared"] = dict(ff=shared)
+    return m
+
+
+# Tiny Fekopel configurations that differ in every size, in the order of the layers and in which optional pieces they
+# have.  Windows are short, so that prompts and decoded tokens alike pass their edges many times.
+TINY_FEKOPEL: Dict[str, dict] = {
+    # heads of 64 with pages of 16: the tensor-core attention kernels in bfloat16; a looped block at the start
+    "fk_a": dict(
+        config=dict(architecture="Fekopel", vocab=150, width=64, norm=dict(eps=1e-5),
+                    layers=[dict(type="attention_2", mixer=_att2(2, 1, 64, 64, 0.2, 40, 5, (5000.0, 16), 6.0), mlp=_fmoe(6, 2, 24, 40, (3, 2), 0.06)),
+                            dict(type="attention", mixer=_att(4, 2, 64, 64, 0.15, 24), mlp=_fmoe(4, 4, 16, None, None, 0.1)),
+                            dict(type="attention", mixer=_att(2, 2, 64, 64, 0.1, 70), mlp=None)],
+                    loop=dict(start=0, stop=2, times=2)),
+        seed=21, init_std=0.1, norm_std=0.1, block_size=16),
+    # values wider and narrower than keys, one key/value head, no loop, rotation of the whole head, a window of one
+    # page and kept keys that fill more than a page, pages of 8
+    "fk_b": dict(
+        config=dict(architecture="Fekopel", vocab=210, width=96, norm=dict(eps=1e-6),
+                    layers=[dict(type="attention", mixer=_att(3, 1, 16, 40, 0.3, 8), mlp=_fmoe(8, 3, 32, 16, (2, 1), 0.05)),
+                            dict(type="attention_2", mixer=_att2(4, 2, 24, 8, 0.25, 19, 11, (100.0, 24), None), mlp=_fmoe(3, 1, 40, 24, None, 0.08)),
+                            dict(type="attention_2", mixer=_att2(2, 2, 32, 48, 0.2, 33, 0, (1e6, 8), 30.0), mlp=None)],
+                    loop=None),
+        seed=22, init_std=0.08, norm_std=0.15, block_size=8),
+    # the whole model is the looped block (three passes); no windows at all; no rotation; pages of 32
+    "fk_c": dict(
+        config=dict(architecture="Fekopel", vocab=131, width=48, norm=dict(eps=2e-5),
+                    layers=[dict(type="attention_2", mixer=_att2(3, 3, 16, 16, 0.25, None, None, None, 4.0), mlp=_fmoe(5, 2, 20, 12, None, 0.04)),
+                            dict(type="attention", mixer=_att(2, 1, 8, 12, 0.5), mlp=None)],
+                    loop=dict(start=0, stop=2, times=3)),
+        seed=23, init_std=0.12, norm_std=0.05, block_size=32),
+    # a block that is "looped" once, in the middle; heads of 128; a window longer than most requests
+    "fk_d": dict(
+        config=dict(architecture="Fekopel", vocab=90, width=32, norm=dict(eps=1e-5),
+                    layers=[dict(type="attention", mixer=_att(1, 1, 128, 128, 0.08, 100), mlp=_fmoe(2, 1, 16, 8, (2, 2), 0.07)),
+                            dict(type="attention_2", mixer=_att2(2, 1, 128, 128, 0.09, 48, 2, (300000.0, 64), 15.0), mlp=_fmoe(4, 2, 8, None, (4, 3), 0.03)),
+                            dict(type="attention", mixer=_att(2, 1, 12, 12, 0.3, 17), mlp=_fmoe(2, 2, 24, 24, None, 0.09))],
+                    loop=dict(start=1, stop=2, times=1)),
+        seed=24, init_std=0.15, norm_std=0.1, block_size=16),
+    # sizes that are multiples of nothing: no 16-byte rows anywhere; a window of three keys
+    "fk_e": dict(
+        config=dict(architecture="Fekopel", vocab=77, width=50, norm=dict(eps=1e-5),
+                    layers=[dict(type="attention_2", mixer=_att2(3, 1, 10, 14, 0.3, 3, 1, (777.0, 6), 9.0), mlp=_fmoe(6, 2, 30, 22, (3, 1), 0.05)),
+                            dict(type="attention", mixer=_att(5, 5, 6, 9, 0.4, 37), mlp=None),
+                            dict(type="attention_2", mixer=_att2(2, 2, 18, 6, 0.2, 21, 30, None, None), mlp=_fmoe(7, 7, 10, 14, None, 0.11))],
+                    loop=dict(start=1, stop=3, times=2)),
+        seed=25, init_std=0.1, norm_std=0.1, block_size=16),
+}
+
+
+def make_fekopel_folder(path: str, name: str, dtype: str = "bfloat16") -> str:
+    from photon_infer_b200.weights import write_random_model
+    t = TINY_FEKOPEL[name]
+    write_random_model(path, t["config"], seed=t["seed"], init_std=t["init_std"], norm_std=t["norm_std"], dtype=dtype)
+    return path
+
+
+_fekopel_cache: Dict[tuple, torch.Tensor] = {}
+_fekopel_models: Dict[str, tuple] = {}
+
+
+def fekopel_plain_model(folder: str):
+    from plain import fekopel_plain
+    if folder not in _fekopel_models:
+        _fekopel_models[folder] = fekopel_plain.read_folder(folder)
+    return _fekopel_models[folder]
+
+
+def fekopel_plain_logits(folder: str, ids: Sequence[int]) -> torch.Tensor:
+    from plain import fekopel_plain
+    key = (folder, tuple(ids))
+    if key not in _fekopel_cache:
+        cfg, tensors = fekopel_plain_model(folder)
+        _fekopel_cache[key] = fekopel_plain.forward(cfg, tensors, list(ids))
+    return _fekopel_cache[key]

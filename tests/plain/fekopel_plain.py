@@ -216,3 +216,40 @@ def forward(config, tensors, tokens, return_layers=False):
     y = layer_norm(x, t64(tensors["final.norm"]), t64(tensors["final.norm.b"]), eps)
     logits = y @ t64(tensors["head"]).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# ----------------------------------------------------------------------------- a model folder
+
+def read_folder(folder):
+    """(config, tensors) of a folder with config.json and model.safetensors (bfloat16 or float32 tensors)."""
+    import json
+    import os
+    import struct
+
+    import numpy as np
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    tensors = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = meta["data_offsets"]
+        if meta["dtype"] == "BF16":
+            t = torch.from_numpy((np.frombuffer(data[a:b], dtype="<u2").astype(np.uint32) << 16).view(np.float32).copy())
+        elif meta["dtype"] == "F32":
+            t = torch.from_numpy(np.frombuffer(data[a:b], dtype="<f4").copy())
+        else:
+            raise ValueError(f"{name}: dtype {meta['dtype']}")
+        tensors[name] = t.reshape(meta["shape"]).to(F)
+    return config, tensors
+
+
+def greedy(config, tensors, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(forward(config, tensors, ids)[-1])))
+    return ids[len(prompt):]
