@@ -21,6 +21,9 @@ Two more workloads go into ``points`` of the same line (``--workloads headline``
 the Finelix decoder (parallel layers of gated linear attention and of attention over a cached latent, dense and
 routed feed-forwards) at two sizes that resemble a real model's layers, beside a Llama decoder of equal width,
 depth and feed-forward size, with each design's own kernels timed alone against their rooflines.
+``--design fekopel`` does the same for the Fekopel decoder (attention with normed queries and keys, a window with kept
+first keys, a sink or bounded scores and an output gate; plain experts behind a grouped router), beside a Llama
+decoder with the same window.
 
 ``--impl reference`` runs lumia431/photon_infer itself where it could be built (``baseline/``); else it
 prints an ``unavailable`` line.
@@ -371,7 +374,7 @@ def main() -> int:
     ap.add_argument("--layers-3b", type=int, default=0, help="fewer layers for the 3B workload (0: all 28)")
     ap.add_argument("--layers-8b", type=int, default=0, help="fewer layers for the 8B workload (0: all 32)")
     ap.add_argument("--batch-8b", type=int, default=8)
-    ap.add_argument("--design", default=None, choices=["finelix"],
+    ap.add_argument("--design", default=None, choices=["finelix", "fekopel"],
                     help="compare this design with a Llama decoder of equal size instead of running the headline")
     ap.add_argument("--design-sizes", default="2048,4096", help="widths to run with --design")
     args = ap.parse_args()
@@ -387,9 +390,9 @@ def main() -> int:
     import torch
 
     hbm_peak, tf_peak, peak_src = peaks()
-    if args.design == "finelix":
-        from photon_infer_b200.kernels.design_bench import run_finelix_comparison
-        print(json.dumps(run_finelix_comparison(args, hbm_peak, tf_peak, peak_src)))
+    if args.design is not None:
+        from photon_infer_b200.kernels.design_bench import run_design_comparison
+        print(json.dumps(run_design_comparison(args.design, args, hbm_peak, tf_peak, peak_src)))
         return 0
     if args.only in ("3b", "8b"):
         fn = run_3b_continuous if args.only == "3b" else run_8b_long

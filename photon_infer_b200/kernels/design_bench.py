@@ -1,6 +1,6 @@
-"""Prefill and decode throughput of the Finelix decoder beside a Llama decoder of equal width, depth and
-feed-forward size (``python bench.py --design finelix``), with the parts of a layer timed alone against their
-rooflines.
+"""Prefill and decode throughput of another design (the Finelix or the Fekopel decoder) beside a Llama decoder of
+equal width, depth and feed-forward size (``python bench.py --design finelix|fekopel``), with the parts of a layer
+timed alone against their rooflines.
 
 Random weights drawn on the device, synthetic token ids, bfloat16.  Per size:
 
@@ -35,10 +35,33 @@ def finelix_config(width: int, layers: int) -> dict:
                 layers=[gla if i % 2 == 0 else lat for i in range(layers)], loop=None)
 
 
-def llama_config(width: int, layers: int) -> dict:
-    return dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=4 * width, num_hidden_layers=layers,
-                num_attention_heads=width // 128, num_key_value_heads=max(1, width // 512), head_dim=128, vocab_size=32000,
-                max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+FEKOPEL_WINDOW = 1024
+
+
+def fekopel_config(width: int, layers: int) -> dict:
+    """Alternating layers of the two attention mixers, heads of 128, four query heads per key/value head, a window of
+    1,024 keys (the second kind keeps its first 4 keys, rotates half of a head and bounds its scores); 16 plain experts
+    of 2 x width, 2 per token from the best 2 of 4 groups, and a shared expert of 2 x width: 12 x width^2 active
+    weights per token, as a gated feed-forward of 4 x width has."""
+    heads, kv = width // 128, max(1, width // 512)
+    mlp = dict(kind="moe", router=dict(experts=16, top=2, scale=1.0, groups=dict(count=4, keep=2)), expert=dict(ff=2 * width),
+               shared=dict(ff=2 * width))
+    a1 = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5,
+                                           mask=dict(size=FEKOPEL_WINDOW)), mlp=mlp)
+    a2 = dict(type="attention_2", mixer=dict(heads=heads, kv_heads=kv, dim=128, vdim=128, scale=128 ** -0.5,
+                                             mask=dict(size=FEKOPEL_WINDOW, keep_first=4), rot=dict(base=10000.0, dims=64),
+                                             softcap=30.0), mlp=mlp)
+    return dict(architecture="Fekopel", vocab=32000, width=width, norm=dict(eps=1e-5),
+                layers=[a2 if i % 2 == 0 else a1 for i in range(layers)], loop=None)
+
+
+def llama_config(width: int, layers: int, window=None) -> dict:
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=4 * width, num_hidden_layers=layers,
+               num_attention_heads=width // 128, num_key_value_heads=max(1, width // 512), head_dim=128, vocab_size=32000,
+               max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    if window:
+        cfg.update(sliding_window=window, layer_types=["sliding_attention"] * layers)
+    return cfg
 
 
 def _time_events(fn, reps: int = 3) -> float:
@@ -99,14 +122,20 @@ def _mixer_numbers(m, kind: str, tokens: int, contexts) -> tuple:
         state = len(contexts) * m.heads * m.dim * m.vdim * 4 * 2
         flops = tokens * (w // 2) * 2 + 5 * tokens * m.heads * m.dim * m.vdim
         return state, flops
+    reach = getattr(m, "window", None)
+    reach = None if reach is None else reach + getattr(m, "keep_first", 0)
+    seen_by = lambda p: p + 1 if reach is None else min(p + 1, reach)      # keys the token at position p reads
+    if kind in ("attention", "normed"):
+        pairs = sum(sum(seen_by(p) for p in range(c)) for c in contexts) if tokens > len(contexts) else sum(seen_by(c - 1) for c in contexts)
+        held = sum(seen_by(c - 1) for c in contexts)
+        dv = getattr(m, "value_dim", m.head_dim)
+        return held * m.n_kv * (m.head_dim + dv) * 2, tokens * (w // 2) * 2 + 2 * m.n_q * (m.head_dim + dv) * pairs
     pairs = sum(c * (c + 1) // 2 for c in contexts) if tokens > len(contexts) else sum(contexts)
     if kind == "latent":
         rows = sum(contexts) * m.width * 2
         flops = tokens * (w // 2) * 2 + 2 * m.heads * (m.width + m.kv_rank) * pairs
         return rows, flops
-    rows = sum(contexts) * 2 * m.n_kv * m.head_dim * 2
-    flops = tokens * (w // 2) * 2 + 4 * m.n_q * m.head_dim * pairs
-    return rows, flops
+    raise ValueError(kind)
 
 
 def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
@@ -115,6 +144,7 @@ def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
     from ..parts.gla import GatedLinearAttention
     from ..parts.latent_attention import LatentAttention
     from ..parts.moe import MoEFeedForward
+    from ..parts.normed_attention import NormedAttention
     model, cache = runner.model, runner.cache
     H = model.spec.hidden_size
     out: Dict[str, dict] = {}
@@ -139,17 +169,22 @@ def _parts(runner, hbm_peak: float, tf_peak: float) -> Dict[str, dict]:
         for i, e in enumerate(model.spec.run):
             block = model.blocks[e.layer]
             m = block.mixer()
-            kind = {GatedLinearAttention: "gla", LatentAttention: "latent", PagedAttention: "attention"}.get(type(m))
+            kind = {GatedLinearAttention: "gla", LatentAttention: "latent", PagedAttention: "attention",
+                    NormedAttention: "normed"}.get(type(m))
+            if kind == "normed":                     # the two kinds of layer are timed apart
+                kind_name = "normed_gated" if m.output_gate else "normed_sink"
+            else:
+                kind_name = kind
             ff = block.parts().get("feed_forward")
             fkind = None if ff is None else ("moe" if isinstance(ff, MoEFeedForward) else "dense")
             lc = runner._layer_caches[i]
-            if kind and (kind, phase) not in seen:
-                seen.add((kind, phase))
+            if kind and (kind_name, phase) not in seen:
+                seen.add((kind_name, phase))
                 us = timer(lambda: m.forward(h, ctx, lc))
                 moved, flops = _mixer_numbers(m, kind, T, contexts)
                 frac = (m.weight_bytes() + moved) / (us * 1e-6) / (hbm_peak * 1e9) if phase == "decode" \
                     else flops / (us * 1e-6) / (tf_peak * 1e12)
-                out[f"{kind}.{phase}"] = {"us": round(us, 1), "frac": round(frac, 4)}
+                out[f"{kind_name}.{phase}"] = {"us": round(us, 1), "frac": round(frac, 4)}
             if fkind and (fkind, phase) not in seen:
                 seen.add((fkind, phase))
                 us = timer(lambda: ff.forward(h, ctx))
@@ -204,19 +239,24 @@ def _throughput(runner, vocab: int, steps: int, warmup: int) -> dict:
 
 
 def run_finelix_comparison(args, hbm_peak: float, tf_peak: float, peak_src: str) -> dict:
+    return run_design_comparison("finelix", args, hbm_peak, tf_peak, peak_src)
+
+
+def run_design_comparison(design: str, args, hbm_peak: float, tf_peak: float, peak_src: str) -> dict:
     from ..cache.manager import CacheManager  # noqa: F401  (import order: the engine pulls in the CUDA side)
     from ..config.engine_options import EngineOptions
     from ..engine.loading import build_cache, random_model
     from ..engine.runner import ModelRunner
     steps, warmup = max(8, min(args.steps, 64)), max(args.warmup, 3)
     layers = {2048: 8, 4096: 4}
-    line = {"design": "finelix", "dtype": args.dtype, "data": "synthetic", "peaks": peak_src,
+    make, window = {"finelix": (finelix_config, None), "fekopel": (fekopel_config, FEKOPEL_WINDOW)}[design]
+    line = {"design": design, "dtype": args.dtype, "data": "synthetic", "peaks": peak_src,
             "workload": {"prefill_tokens": PREFILL, "decode_batch": BATCH, "decode_context": PROMPT, "steps": steps,
                          "warmup": warmup}, "sizes": {}}
     for width in [int(w) for w in args.design_sizes.split(",") if w]:
         n_layers = layers.get(width, 4)
         point = {"layers": n_layers}
-        for name, cfg in (("finelix", finelix_config(width, n_layers)), ("llama", llama_config(width, n_layers))):
+        for name, cfg in ((design, make(width, n_layers)), ("llama", llama_config(width, n_layers, window))):
             print(f"[bench] {name} width {width}, {n_layers} layers", file=sys.stderr, flush=True)
             model = random_model(cfg, args.dtype, seed=0)
             options = EngineOptions(dtype=args.dtype, block_size=args.block_size,
