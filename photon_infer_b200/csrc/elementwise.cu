@@ -327,12 +327,37 @@ __global__ void activation_kernel(const T* x, T* out, size_t total, int act) {
   for (; idx < total; idx += stride) out[idx] = from_f32<T>(glu_act(to_f32(x[idx]), act));
 }
 
+// The same, 16 bytes per load and store: total a multiple of the elements in 16 bytes, aligned pointers.
+template <typename T>
+__global__ void activation_vec_kernel(const T* x, T* out, size_t total_vecs, int act) {
+  constexpr int N = 16 / sizeof(T);
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vecs; idx += stride) {
+    const uint4 v = reinterpret_cast<const uint4*>(x)[idx];
+    const T* p = reinterpret_cast<const T*>(&v);
+    uint4 o;
+    T* q = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int e = 0; e < N; ++e) q[e] = from_f32<T>(glu_act(to_f32(p[e]), act));
+    reinterpret_cast<uint4*>(out)[idx] = o;
+  }
+}
+
 PHOTON_API int photon_activation(const void* x, void* out, int dtype, long total, int act, cudaStream_t stream) {
   if (act != PHOTON_ACT_SILU && act != PHOTON_ACT_GELU_TANH && act != PHOTON_ACT_GELU) return PHOTON_ERR_ARGUMENT;
   if (total <= 0) return 0;
-  size_t blocks = ((size_t)total + 255) / 256;
+  const int n = dtype == PHOTON_BF16 ? 8 : 4;
+  const bool vec = (total % n == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  const size_t work = vec ? (size_t)total / n : (size_t)total;
+  size_t blocks = (work + 255) / 256;
   const size_t cap = (size_t)photon_sm_count() * 16;
   if (blocks > cap) blocks = cap;
+  if (vec) {
+    if (dtype == PHOTON_BF16) activation_vec_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)x, (bf16*)out, work, act);
+    else activation_vec_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (float*)out, work, act);
+    return launch_status();
+  }
   if (dtype == PHOTON_BF16) activation_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)x, (bf16*)out, (size_t)total, act);
   else activation_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)total, act);
   return launch_status();
@@ -352,13 +377,40 @@ __global__ void gate_mul_kernel(TX* x, long ldx, const TG* g, long ldg, int W, s
   }
 }
 
+// Four elements per thread and step: W and both row strides multiples of 4, 16-byte aligned pointers (8-byte for
+// bfloat16 rows).
+template <typename TX, typename TG>
+__global__ void gate_mul_vec_kernel(TX* x, long ldx, const TG* g, long ldg, int W, size_t total_quads) {
+  const int per_row = W / 4;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_quads; idx += stride) {
+    const size_t t = idx / per_row;
+    const int i = (int)(idx - t * per_row) * 4;
+    float xv[4], gv[4];
+    Quad<TX>::load(x + t * ldx + i, xv);
+    Quad<TG>::load(g + t * ldg + i, gv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) xv[e] = xv[e] / (1.0f + expf(-gv[e]));
+    Quad<TX>::store(x + t * ldx + i, xv);
+  }
+}
+
 PHOTON_API int photon_gate_mul(void* x, long ldx, int x_dtype, const void* g, long ldg, int g_dtype, int T, int W,
                                cudaStream_t stream) {
   const size_t total = (size_t)T * W;
   if (total == 0) return 0;
-  size_t blocks = (total + 255) / 256;
+  const bool vec = (W % 4 == 0) && (ldx % 4 == 0) && (ldg % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)g % 16 == 0);
+  size_t blocks = ((vec ? total / 4 : total) + 255) / 256;
   const size_t cap = (size_t)photon_sm_count() * 16;
   if (blocks > cap) blocks = cap;
+  if (vec) {
+    if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_BF16) gate_mul_vec_kernel<bf16, bf16><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const bf16*)g, ldg, W, total / 4);
+    else if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_F32) gate_mul_vec_kernel<bf16, float><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const float*)g, ldg, W, total / 4);
+    else if (x_dtype == PHOTON_F32 && g_dtype == PHOTON_F32) gate_mul_vec_kernel<float, float><<<(int)blocks, 256, 0, stream>>>((float*)x, ldx, (const float*)g, ldg, W, total / 4);
+    else return PHOTON_ERR_ARGUMENT;
+    return launch_status();
+  }
   if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_BF16) gate_mul_kernel<bf16, bf16><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const bf16*)g, ldg, W, total);
   else if (x_dtype == PHOTON_BF16 && g_dtype == PHOTON_F32) gate_mul_kernel<bf16, float><<<(int)blocks, 256, 0, stream>>>((bf16*)x, ldx, (const float*)g, ldg, W, total);
   else if (x_dtype == PHOTON_F32 && g_dtype == PHOTON_F32) gate_mul_kernel<float, float><<<(int)blocks, 256, 0, stream>>>((float*)x, ldx, (const float*)g, ldg, W, total);

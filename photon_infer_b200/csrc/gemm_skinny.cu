@@ -32,6 +32,7 @@
 #define EPI_BF16 0
 #define EPI_F32 1
 #define EPI_SWIGLU 2
+#define EPI_GELU 4                    // bfloat16 out, the exact gelu 0.5 y (1 + erf(y / sqrt 2)) of every output
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 r;
@@ -218,6 +219,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     if (EPI == EPI_SWIGLU) {
       const float s = v0 / (1.0f + __expf(-v0));
       ((bf16*)out)[(size_t)tok * ldo + row] = __float2bfloat16_rn(s * v1);
+    } else if (EPI == EPI_GELU) {
+      ((bf16*)out)[(size_t)tok * ldo + row] = __float2bfloat16_rn(0.5f * v0 * (1.0f + erff(v0 * 0.7071067811865476f)));
     } else if (EPI == EPI_F32) {
       ((float*)out)[(size_t)tok * ldo + row] = v0;
     } else {
@@ -276,7 +279,7 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   return st;
 }
 
-// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).
+// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]), 4 exact gelu of every output (bfloat16).
 // Needs K % 8 == 0 and 16-byte aligned rows of x and W; M <= 64 (32 with SwiGLU).
 // scratch (float) and tickets (int, all zero between launches) serve the split of K over blocks;
 // without them K is not split.  Launches that share them must not overlap on the device.
@@ -291,6 +294,7 @@ PHOTON_API int photon_skinny_gemm(const void* x, long ldx, const void* W, long l
     case EPI_BF16: return skinny_launch<EPI_BF16>(x, ldx, W, ldw, out, ldo, M, N, K, scratch, scratch_floats, tickets, num_tickets, stream);
     case EPI_F32: return skinny_launch<EPI_F32>(x, ldx, W, ldw, out, ldo, M, N, K, scratch, scratch_floats, tickets, num_tickets, stream);
     case EPI_SWIGLU: return skinny_launch<EPI_SWIGLU>(x, ldx, W, ldw, out, ldo, M, N, K, scratch, scratch_floats, tickets, num_tickets, stream);
+    case EPI_GELU: return skinny_launch<EPI_GELU>(x, ldx, W, ldw, out, ldo, M, N, K, scratch, scratch_floats, tickets, num_tickets, stream);
   }
   return PHOTON_ERR_ARGUMENT;
 }

@@ -42,6 +42,7 @@
 #define TC_EPI_BF16 0
 #define TC_EPI_F32 1
 #define TC_EPI_SWIGLU 2
+#define TC_EPI_GELU 4                 // bfloat16 out, the exact gelu 0.5 y (1 + erf(y / sqrt 2)) of every output
 
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; tiles are numbered with the
 // N index fastest.  Two accumulators of TC_BN columns alternate, so the epilogue of one tile runs while
@@ -171,7 +172,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float g = __uint_as_float(v[j]);
-              y[j] = (EPI == TC_EPI_SWIGLU) ? __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j]) : g;
+              y[j] = (EPI == TC_EPI_SWIGLU) ? __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j])
+                                             : (EPI == TC_EPI_GELU ? 0.5f * g * (1.0f + erff(g * 0.7071067811865476f)) : g);
             }
             if (col0 + 32 <= ncols && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -207,7 +209,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).
+// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]), 4 exact gelu of every output (bfloat16).
 // Needs 16-byte aligned bases and row strides that are a multiple of 8 elements (TMA), K a multiple of 8.
 PHOTON_API int photon_gemm_tc(const void* x, long ldx, const void* W, long ldw, void* out, long ldo, int M, int N,
                               int K, int epilogue, int* err, cudaStream_t stream) {
@@ -242,6 +244,8 @@ PHOTON_API int photon_gemm_tc(const void* x, long ldx, const void* W, long ldw, 
     if (e0 != cudaSuccess) return (int)e0;
     if (e1 != cudaSuccess) return (int)e1;
     if (e2 != cudaSuccess) return (int)e2;
+    cudaError_t e4 = cudaFuncSetAttribute(gemm_tc_kernel<TC_EPI_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    if (e4 != cudaSuccess) return (int)e4;
     attr_done = true;
   }
   switch (epilogue) {
@@ -251,6 +255,8 @@ PHOTON_API int photon_gemm_tc(const void* x, long ldx, const void* W, long ldw, 
       return launch_pdl(gemm_tc_kernel<TC_EPI_F32>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
     case TC_EPI_SWIGLU:
       return launch_pdl(gemm_tc_kernel<TC_EPI_SWIGLU>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
+    case TC_EPI_GELU:
+      return launch_pdl(gemm_tc_kernel<TC_EPI_GELU>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
     default:
       return PHOTON_ERR_ARGUMENT;
   }

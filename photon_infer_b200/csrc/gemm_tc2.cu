@@ -43,6 +43,7 @@
 #define T2_EPI_BF16 0
 #define T2_EPI_F32 1
 #define T2_EPI_SWIGLU 2
+#define T2_EPI_GELU 4                 // bfloat16 out, the exact gelu 0.5 y (1 + erf(y / sqrt 2)) of every output
 #define T2_EPI_QKV 3                  // rows of q | k | v: q and k rotated, q to `out`, k and v into the paged cache
 
 // What the QKV epilogue needs beside the product (formulas: include/photon/ops/kernels/rope_kernel.hpp:54-84 for
@@ -283,7 +284,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float g = __uint_as_float(v[j]);
-              y[j] = (EPI == T2_EPI_SWIGLU) ? __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j]) : g;
+              y[j] = (EPI == T2_EPI_SWIGLU) ? __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j])
+                                             : (EPI == T2_EPI_GELU ? 0.5f * g * (1.0f + erff(g * 0.7071067811865476f)) : g);
             }
             if (col0 + 32 <= ncols && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -332,7 +334,7 @@ static int t2_launch(const void* x, long ldx, const void* W, long ldw, void* out
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return PHOTON_ERR_UNSUPPORTED;
   if (epilogue == T2_EPI_SWIGLU && (N & 1)) return PHOTON_ERR_ARGUMENT;
-  if (epilogue < 0 || epilogue > 3) return PHOTON_ERR_ARGUMENT;
+  if (epilogue < 0 || epilogue > 4) return PHOTON_ERR_ARGUMENT;
   const int I = N / 2;
   CUtensorMap map_a, map_w;
   int st = make_map(&map_a, x, M, K, ldx, T2_BM);
@@ -354,12 +356,13 @@ static int t2_launch(const void* x, long ldx, const void* W, long ldw, void* out
   const int pairs = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e[4];
+    cudaError_t e[5];
     e[0] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
     e[1] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
     e[2] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
     e[3] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
-    for (int i = 0; i < 4; ++i) if (e[i] != cudaSuccess) return (int)e[i];
+    e[4] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+    for (int i = 0; i < 5; ++i) if (e[i] != cudaSuccess) return (int)e[i];
     attr_done = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -377,6 +380,7 @@ static int t2_launch(const void* x, long ldx, const void* W, long ldw, void* out
     case T2_EPI_BF16: e = T2_GO(T2_EPI_BF16); break;
     case T2_EPI_F32: e = T2_GO(T2_EPI_F32); break;
     case T2_EPI_SWIGLU: e = T2_GO(T2_EPI_SWIGLU); break;
+    case T2_EPI_GELU: e = T2_GO(T2_EPI_GELU); break;
     default: e = T2_GO(T2_EPI_QKV); break;
   }
 #undef T2_GO
@@ -384,10 +388,11 @@ static int t2_launch(const void* x, long ldx, const void* W, long ldw, void* out
   return launch_status();
 }
 
-// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).  Same requirements as photon_gemm_tc.
+// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]), 4 exact gelu of every output (bfloat16).
+// Same requirements as photon_gemm_tc.
 PHOTON_API int photon_gemm_tc2(const void* x, long ldx, const void* W, long ldw, void* out, long ldo, int M, int N,
                                int K, int epilogue, int* err, cudaStream_t stream) {
-  if (epilogue < 0 || epilogue > 2) return PHOTON_ERR_ARGUMENT;
+  if (epilogue < 0 || epilogue > 4 || epilogue == T2_EPI_QKV) return PHOTON_ERR_ARGUMENT;
   T2Qkv Q = {};
   return t2_launch(x, ldx, W, ldw, out, ldo, M, N, K, epilogue, Q, err, stream);
 }

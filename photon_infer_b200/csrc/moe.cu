@@ -51,7 +51,43 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
   }
   __syncthreads();
   if (threadIdx.x == 0 && Wsg) shared_gate[t] = 1.0f / (1.0f + expf(-lg[E]));
-  if (threadIdx.x == 0 && mode == 1) {
+  if (warp == 0 && mode == 1 && E <= 32) {
+    // The same rules as the serial form below with one lane per expert: maxima and sums by shuffles, a choice is the
+    // lowest lane that holds the maximum (so ties go to the lower index).  top <= E <= 32.
+    const unsigned full = 0xffffffffu;
+    const bool live = lane < E;
+    const float z = live ? lg[lane] : -INFINITY;
+    const float mx = warp_max(z);
+    const float p = live ? expf(z - mx) : 0.f;
+    const float score = p / warp_sum(p);
+    float cand = live ? score : -1.f;
+    if (n_groups > 1 && keep_groups < n_groups) {
+      const int per = E / n_groups;
+      float gs = -1.f;                                   // lane g < n_groups: the best score of group g
+      for (int g = 0; g < n_groups; ++g) {
+        const float m = warp_max((live && lane / per == g) ? score : -1.f);
+        if (lane == g) gs = m;
+      }
+      unsigned kept = 0u;                                // n_groups <= 32 here, because E <= 32
+      for (int r = 0; r < keep_groups; ++r) {
+        const float m = warp_max(gs);
+        const int g = __ffs(__ballot_sync(full, gs == m && lane < n_groups)) - 1;
+        kept |= 1u << g;
+        if (lane == g) gs = -2.f;
+      }
+      if (live && !((kept >> (lane / per)) & 1u)) cand = -1.f;
+    }
+    float sum = 0.f, mine = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const float m = warp_max(cand);
+      const int best = __ffs(__ballot_sync(full, cand == m && live)) - 1;
+      if (lane == j) mine = m;
+      if (lane == best) cand = -2.f;
+      sum += m;
+      if (lane == 0) { ids[(size_t)t * top + j] = best; atomicAdd(&counts[best], 1); }
+    }
+    if (lane < top) weights[(size_t)t * top + lane] = mine / (sum + 1e-20f) * route_scale;
+  } else if (threadIdx.x == 0 && mode == 1) {
     // scores: softmax over ALL experts.  Groups of E / n_groups neighbours: a group's score is its largest score,
     // and only experts of the keep_groups best groups can be chosen.  Weights: the chosen scores over their sum,
     // times route_scale.  Ties go to the lower index everywhere.

@@ -682,12 +682,12 @@ def _skinny_scratch(device):
 
 def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16") -> None:
     """``out = x @ weight^T`` for few rows, the weights streamed once.  ``epilogue``: ``"bf16"``,
-    ``"f32"`` (float output) or ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out`` is
-    ``[M, I]`` with ``silu(gate) * up``)."""
+    ``"f32"`` (float output), ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out`` is
+    ``[M, I]`` with ``silu(gate) * up``) or ``"gelu"`` (the exact gelu of every output, bfloat16)."""
     _cuda(x, weight, out)
     M, K = x.shape
     N = weight.shape[0]
-    code = {"bf16": 0, "f32": 1, "swiglu": 2}[epilogue]
+    code = {"bf16": 0, "f32": 1, "swiglu": 2, "gelu": 4}[epilogue]
     cols = N // 2 if epilogue == "swiglu" else N
     want = torch.float32 if epilogue == "f32" else torch.bfloat16
     if not skinny_gemm_supported(x, weight, epilogue == "swiglu") or weight.shape[1] != K:
@@ -784,6 +784,23 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "s
     return out
 
 
+def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str) -> torch.Tensor:
+    """``act(x W^T)`` for an ungated feed-forward.  bfloat16 with the exact gelu: the activation rides in the
+    epilogue of the product where this package's own kernels run it (few rows: the weight-streaming kernel; enough
+    tiles: tcgen05); otherwise the product followed by the activation kernel."""
+    M, N = x.shape[0], weight.shape[0]
+    if act == "gelu" and x.dtype == torch.bfloat16:
+        if M <= SKINNY_MAX_ROWS and skinny_gemm_supported(x, weight):
+            out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            skinny_gemm(x, weight, out, "gelu")
+            return out
+        if gemm_tc_supported(x, weight) and gemm_tc_tiles(M, N) >= TC_MIN_TILES:
+            out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            gemm_tc(x, weight, out, "gelu", pair=M >= TC_PAIR_MIN_ROWS)
+            return out
+    return activation(linear(x, weight), act)
+
+
 _error_words = {}
 
 
@@ -818,13 +835,13 @@ def gemm_tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16",
             err: Optional[torch.Tensor] = None, pair: bool = False) -> None:
     """``out = x @ weight^T`` on the tcgen05 tensor cores (TMA operands, accumulator in tensor memory).
-    ``epilogue``: ``"bf16"``, ``"f32"`` or ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out``
-    is ``[M, I]``).  ``pair``: tiles of 256 x 256 on pairs of SMs (``gemm_tc2.cu``) instead of 128 x 256
+    ``epilogue``: ``"bf16"``, ``"f32"``, ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out``
+    is ``[M, I]``) or ``"gelu"`` (the exact gelu of every output).  ``pair``: tiles of 256 x 256 on pairs of SMs (``gemm_tc2.cu``) instead of 128 x 256
     on one."""
     _cuda(x, weight, out, err)
     M, K = x.shape
     N = weight.shape[0]
-    code = {"bf16": 0, "f32": 1, "swiglu": 2}[epilogue]
+    code = {"bf16": 0, "f32": 1, "swiglu": 2, "gelu": 4}[epilogue]
     cols = N // 2 if epilogue == "swiglu" else N
     want = torch.float32 if epilogue == "f32" else torch.bfloat16
     if not gemm_tc_supported(x, weight) or weight.shape[1] != K:

@@ -101,7 +101,7 @@ class MoEFeedForward(FeedForward):
     def _shared(self, h: torch.Tensor) -> torch.Tensor:
         if self.gated:
             return project(ops.linear_swiglu(h, self.shared_gate_up, self.shared_activation), self.shared_down)
-        return project(ops.activation(project(h, self.shared_gate_up), self.shared_activation), self.shared_down)
+        return project(ops.linear_act(h, self.shared_gate_up, self.shared_activation), self.shared_down)
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = h.shape

@@ -9,9 +9,8 @@ key).  The softmax may have a sink: one more key with score 0 and no value, ``p_
 The heads' outputs may be multiplied by ``sigmoid(W_g h)`` (``h`` the mixer's input) before the output projection.
 A value may have another width than a key.
 
-Kernels of a step: ONE product for q, k, v (and the gate) that hands over unrounded 32-bit sums; one pass that norms
-and rotates in 32-bit (angles in 64-bit) and writes queries, keys and values (``qk_norm.cu``); attention; the gate;
-the output product.  Prompt portions, decoded tokens and mixed batches take the same path.
+Kernels of a step: ONE product for q, k, v (and the gate); one pass that norms and rotates in 32-bit (angles in
+64-bit) and writes queries, keys and values (``qk_norm.cu``); attention; the gate; the output product.  Prompt portions, decoded tokens and mixed batches take the same path.
 """
 from __future__ import annotations
 
@@ -113,7 +112,7 @@ class NormedAttention(Mixer):
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         T = h.shape[0]
         nq, nk, nv, ng = self._sections
-        rows = project(h, self.w_in, out_dtype=torch.float32)            # unrounded sums for the norm that follows
+        rows = project(h, self.w_in)
         q = torch.empty((T, nq), dtype=h.dtype, device=h.device)
         group = ctx.groups[cache.group]
         store = not cache.shared and cache.k is not None

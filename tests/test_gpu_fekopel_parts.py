@@ -80,6 +80,24 @@ def test_output_gate(dtype):
     xd = x.to(DEV).clone()
     ops.gate_mul(xd, z.to(DEV)[:, 20:70])                      # a 32-bit gate in a view with a row stride
     assert rel_err(xd.float().cpu(), x.double() * torch.sigmoid(z.double()[:, 20:70])) < (1e-6 if dtype == torch.float32 else 5e-3)
+    x4, z4 = torch.randn(6, 64, generator=g).to(dtype), torch.randn(6, 200, generator=g)      # rows of four: the vector path
+    xd = x4.to(DEV).clone()
+    ops.gate_mul(xd, z4.to(DEV)[:, 128:192])
+    assert rel_err(xd.float().cpu(), x4.double() * torch.sigmoid(z4.double()[:, 128:192])) < (1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype,rows,n,k", [(torch.bfloat16, 3, 96, 64), (torch.bfloat16, 40, 88, 56), (torch.bfloat16, 512, 6144, 256),
+                                            (torch.bfloat16, 200, 6144 * 2, 128), (torch.float32, 5, 30, 20), (torch.bfloat16, 7, 33, 50)])
+def test_product_with_gelu_behind_it(dtype, rows, n, k):
+    """Few rows (the weight-streaming kernel), many tiles (tcgen05, on one SM and on pairs) and in between (the
+    library's product, then the activation kernel): the exact gelu of every output."""
+    from photon_infer_b200.kernels import ops
+    g = torch.Generator().manual_seed(rows)
+    x, w = torch.randn(rows, k, generator=g).to(dtype), (0.2 * torch.randn(n, k, generator=g)).to(dtype)
+    got = ops.linear_act(x.to(DEV), w.to(DEV), "gelu").float().cpu()
+    assert rel_err(got, plain.gelu_erf(x.double() @ w.double().T)) < (2e-6 if dtype == torch.float32 else 6e-3)
+    z = torch.randn(5, 24 if dtype == torch.bfloat16 else 7, generator=g).to(dtype)      # the vector path and the plain one
+    assert rel_err(ops.activation(z.to(DEV).clone(), "gelu").float().cpu(), plain.gelu_erf(z.double())) < (1e-6 if dtype == torch.float32 else 5e-3)
 
 
 # ----------------------------------------------------------------------------- query/key norm, rotation, cache write
@@ -338,7 +356,8 @@ def test_mixer_in_portions(dtype, kind, shape):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [dict(E=16, top=4, groups=(4, 3), scale=1.5), dict(E=6, top=2, groups=(3, 1), scale=0.5),
                                    dict(E=5, top=5, groups=None, scale=2.0), dict(E=8, top=1, groups=(8, 2), scale=1.0),
-                                   dict(E=12, top=3, groups=(1, 1), scale=1.0)])
+                                   dict(E=12, top=3, groups=(1, 1), scale=1.0),
+                                   dict(E=40, top=3, groups=(5, 2), scale=0.7), dict(E=32, top=32, groups=(4, 4), scale=1.0)])   # more experts than lanes: one thread walks them
 def test_router_with_groups(dtype, shape):
     from photon_infer_b200.kernels import ops
     E, top, H, T = shape["E"], shape["top"], 40, 64
