@@ -19,39 +19,69 @@
 #define MOE_BM 32          // rows of a tile of the grouped products
 
 // ---------------------------------------------------------------- router
+// A block owns `tok` consecutive tokens (at most its number of warps, at most 8): a warp takes every nwarp-th row of
+// the router and forms that row's logit for all of the block's tokens at once, so the row is read once per block.
+// Then warp i chooses for token i.  A logit's sum has the same order whatever `tok` is.  Measured on B200 with 2,048
+// tokens, 16 experts, rows of 2,048 (the call with its memset): one token per block 57 us, two 47, four 41, eight 59
+// (256 blocks, each walking its rows in sequence, are too few); 8 tokens: one per block 22 us, eight in one block 61.
+#define MOE_ROUTE_TOK 8
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ Wr,
                                  const void* __restrict__ bias, int bias_bf16, int H, int E, int top,
                                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T_,
                                  int mode, int n_groups, int keep_groups, float route_scale,
-                                 const T* __restrict__ Wsg, float* __restrict__ shared_gate) {
-  extern __shared__ float logits[];                     // E (+ 1: the logit of the shared expert's gate)
+                                 const T* __restrict__ Wsg, float* __restrict__ shared_gate, int tok) {
+  extern __shared__ float logits[];                     // per token: E (+ 1: the shared expert's gate) + n_groups flags
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  const int t = blockIdx.x;                              // one block per token, its warps share the experts out
-  float* lg = logits;
-  const T* x = h + (size_t)t * h_stride;
+  const int t0 = blockIdx.x * tok;
+  const int ntok = min(tok, T_ - t0);
+  const int LS = E + 1 + n_groups;
   constexpr int V = 16 / sizeof(T);                      // elements of a 16-byte load
-  const bool vec = (H % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)Wr % 16 == 0);
+  const bool vec = (H % V == 0) && ((uintptr_t)h % 16 == 0) && (h_stride % V == 0) && ((uintptr_t)Wr % 16 == 0) &&
+                   ((uintptr_t)Wsg % 16 == 0);
   for (int e = warp; e < E + (Wsg ? 1 : 0); e += nwarp) {
     const T* w = e < E ? Wr + (size_t)e * H : Wsg;
-    float acc = 0.f;
+    float acc[MOE_ROUTE_TOK];
+#pragma unroll
+    for (int i = 0; i < MOE_ROUTE_TOK; ++i) acc[i] = 0.f;
     if (vec) {
       for (int k = lane * V; k < H; k += 32 * V) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(x + k), wv = *reinterpret_cast<const uint4*>(w + k);
-        const T* xp = reinterpret_cast<const T*>(&xv);
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
         const T* wp = reinterpret_cast<const T*>(&wv);
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc = fmaf(to_f32(xp[i]), to_f32(wp[i]), acc);
+        for (int i = 0; i < MOE_ROUTE_TOK; ++i) {
+          if (i < ntok) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(h + (size_t)(t0 + i) * h_stride + k);
+            const T* xp = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+            for (int u = 0; u < V; ++u) acc[i] = fmaf(to_f32(xp[u]), to_f32(wp[u]), acc[i]);
+          }
+        }
       }
     } else {
-      for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(x[k]), to_f32(w[k]), acc);
+      for (int k = lane; k < H; k += 32) {
+        const float wk = to_f32(w[k]);
+#pragma unroll
+        for (int i = 0; i < MOE_ROUTE_TOK; ++i)
+          if (i < ntok) acc[i] = fmaf(to_f32(h[(size_t)(t0 + i) * h_stride + k]), wk, acc[i]);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) lg[e] = acc + ((bias && e < E) ? load_w(bias, bias_bf16, e) : 0.f);
+    const float add = (bias && e < E) ? load_w(bias, bias_bf16, e) : 0.f;
+#pragma unroll
+    for (int i = 0; i < MOE_ROUTE_TOK; ++i) {
+      if (i < ntok) {
+        const float v = warp_sum(acc[i]);
+        if (lane == 0) logits[i * LS + e] = v + add;
+      }
+    }
   }
   __syncthreads();
-  if (threadIdx.x == 0 && Wsg) shared_gate[t] = 1.0f / (1.0f + expf(-lg[E]));
-  if (warp == 0 && mode == 1 && E <= 32) {
+  if (warp >= ntok) return;
+  const int t = t0 + warp;                               // this warp's token
+  float* lg = logits + warp * LS;
+  const bool first = lane == 0;
+  if (first && Wsg) shared_gate[t] = 1.0f / (1.0f + expf(-lg[E]));
+  if (mode == 1 && E <= 32) {
     // The same rules as the serial form below with one lane per expert: maxima and sums by shuffles, a choice is the
     // lowest lane that holds the maximum (so ties go to the lower index).  top <= E <= 32.
     const unsigned full = 0xffffffffu;
@@ -87,7 +117,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
       if (lane == 0) { ids[(size_t)t * top + j] = best; atomicAdd(&counts[best], 1); }
     }
     if (lane < top) weights[(size_t)t * top + lane] = mine / (sum + 1e-20f) * route_scale;
-  } else if (threadIdx.x == 0 && mode == 1) {
+  } else if (first && mode == 1) {
     // scores: softmax over ALL experts.  Groups of E / n_groups neighbours: a group's score is its largest score,
     // and only experts of the keep_groups best groups can be chosen.  Weights: the chosen scores over their sum,
     // times route_scale.  Ties go to the lower index everywhere.
@@ -98,21 +128,22 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
     for (int e = 0; e < E; ++e) lg[e] /= den;
     if (n_groups > 1 && keep_groups < n_groups) {
       const int per = E / n_groups;
-      unsigned long long kept = 0ull;                    // n_groups <= 64
+      float* kept = lg + E + 1;                          // n_groups flags behind the logits
+      for (int g = 0; g < n_groups; ++g) kept[g] = 0.f;
       for (int r = 0; r < keep_groups; ++r) {
         int bg = -1;
         float bs = -1.f;
         for (int g = 0; g < n_groups; ++g) {
-          if (kept >> g & 1ull) continue;
+          if (kept[g] != 0.f) continue;
           float gs = -1.f;
           for (int i = 0; i < per; ++i) gs = fmaxf(gs, lg[g * per + i]);
           if (gs > bs) { bs = gs; bg = g; }
         }
-        kept |= 1ull << bg;
+        kept[bg] = 1.f;
       }
       // a score of an expert outside the kept groups is hidden behind a negative number; it is not used again
       for (int g = 0; g < n_groups; ++g)
-        if (!(kept >> g & 1ull))
+        if (kept[g] == 0.f)
           for (int i = 0; i < per; ++i) lg[g * per + i] = -1.f;
     }
     float sum = 0.f;
@@ -131,7 +162,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, long h_stride, const T
     }
     for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] = weights[(size_t)t * top + j] / (sum + 1e-20f) * route_scale;
   }
-  if (threadIdx.x == 0 && mode == 0) {
+  if (first && mode == 0) {
     float chosen_max = -INFINITY;
     for (int j = 0; j < top; ++j) {
       int best = -1;
@@ -177,23 +208,24 @@ PHOTON_API int photon_moe_route_ex(const void* h, long h_stride, int dtype, cons
   if (E <= 0 || top <= 0 || top > E || H <= 0) return PHOTON_ERR_ARGUMENT;
   if (mode != 0 && mode != 1) return PHOTON_ERR_ARGUMENT;
   if (n_groups < 1 || keep_groups < 1 || keep_groups > n_groups || E % n_groups) return PHOTON_ERR_ARGUMENT;
-  if (n_groups > 64) return PHOTON_ERR_UNSUPPORTED;
   if (mode == 1 && n_groups > 1 && (long)keep_groups * (E / n_groups) < top) return PHOTON_ERR_ARGUMENT;
   if ((Wsg == nullptr) != (shared_gate == nullptr)) return PHOTON_ERR_ARGUMENT;
   const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
-  const size_t smem = (size_t)(E + 1) * sizeof(float);
+  // few tokens (a decode step): one per block, so that every token's logits form on an SM of their own
+  const int tok = T_ >= 64 ? (warps < 4 ? warps : 4) : 1;
+  const size_t smem = (size_t)tok * (E + 1 + n_groups) * sizeof(float);
   if (smem > 48 * 1024) return PHOTON_ERR_UNSUPPORTED;
   cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
-  const int blocks = T_;
+  const int blocks = (T_ + tok - 1) / tok;
   if (dtype == PHOTON_BF16)
     moe_route_kernel<bf16><<<blocks, warps * 32, smem, stream>>>((const bf16*)h, h_stride, (const bf16*)Wr, bias,
                                                                 bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_,
-                                                                mode, n_groups, keep_groups, route_scale, (const bf16*)Wsg, shared_gate);
+                                                                mode, n_groups, keep_groups, route_scale, (const bf16*)Wsg, shared_gate, tok);
   else
     moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>((const float*)h, h_stride, (const float*)Wr, bias,
                                                                  bias_dtype == PHOTON_BF16, H, E, top, ids, weights, counts, T_,
-                                                                 mode, n_groups, keep_groups, route_scale, (const float*)Wsg, shared_gate);
+                                                                 mode, n_groups, keep_groups, route_scale, (const float*)Wsg, shared_gate, tok);
   return launch_status();
 }
 

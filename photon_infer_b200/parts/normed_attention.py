@@ -70,6 +70,9 @@ class NormedAttention(Mixer):
                 mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
             if self._tc_ok(dtype):
                 mods.append(("attention_tc", {"HEAD_DIM": self.head_dim}))
+            if self._flash_ok(dtype) and not (self.keep_first or self.sink or self.softcap) and self.head_dim in (64, 128) \
+                    and self.n_q // self.n_kv <= 16:
+                mods.append(("attention_decode", {"HEAD_DIM": self.head_dim}))     # long contexts without any of the rules
         return mods
 
     def _flash_ok(self, dtype) -> bool:

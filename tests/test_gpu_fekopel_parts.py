@@ -247,7 +247,8 @@ LENGTHS, COUNTS = [33, 150, 97, 200, 1, 300], [33, 50, 1, 2, 1, 1]
 @pytest.mark.parametrize("kernel,dtype,d,dv,page", [("general", torch.float32, 10, 14, 8), ("general", torch.float32, 64, 64, 16),
                                                     ("general", torch.bfloat16, 24, 8, 16), ("tensor", torch.bfloat16, 64, 64, 16),
                                                     ("tensor", torch.bfloat16, 128, 128, 16), ("tensor", torch.bfloat16, 64, 64, 64),
-                                                    ("tensor", torch.bfloat16, 32, 32, 8)])
+                                                    ("tensor", torch.bfloat16, 32, 32, 8), ("tensor", torch.bfloat16, 48, 48, 16),
+                                                    ("tensor", torch.bfloat16, 96, 96, 32), ("general", torch.bfloat16, 256, 64, 16)])
 def test_attention_rules_in_every_kernel(rule, heads, kernel, dtype, d, dv, page):
     nq, nkv = heads
     st = _Step(LENGTHS, COUNTS, nq, nkv, d, dv, page, dtype, seed=nq * 100 + d, std=1.0 if d < 64 else 0.5)
@@ -357,7 +358,8 @@ def test_mixer_in_portions(dtype, kind, shape):
 @pytest.mark.parametrize("shape", [dict(E=16, top=4, groups=(4, 3), scale=1.5), dict(E=6, top=2, groups=(3, 1), scale=0.5),
                                    dict(E=5, top=5, groups=None, scale=2.0), dict(E=8, top=1, groups=(8, 2), scale=1.0),
                                    dict(E=12, top=3, groups=(1, 1), scale=1.0),
-                                   dict(E=40, top=3, groups=(5, 2), scale=0.7), dict(E=32, top=32, groups=(4, 4), scale=1.0)])   # more experts than lanes: one thread walks them
+                                   dict(E=40, top=3, groups=(5, 2), scale=0.7), dict(E=32, top=32, groups=(4, 4), scale=1.0),
+                                   dict(E=140, top=2, groups=(70, 3), scale=1.0)])   # more experts than lanes: one thread walks them
 def test_router_with_groups(dtype, shape):
     from photon_infer_b200.kernels import ops
     E, top, H, T = shape["E"], shape["top"], 40, 64
