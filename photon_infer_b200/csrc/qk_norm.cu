@@ -15,7 +15,25 @@
 
 #define QKN_WARPS 4
 
-template <typename TI, typename TO>
+// Four consecutive elements as one load or store (16 bytes of float, 8 of bfloat16).
+__device__ __forceinline__ void qkn_load4(const float* p, float* f) { const float4 r = *reinterpret_cast<const float4*>(p); f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w; }
+__device__ __forceinline__ void qkn_load4(const bf16* p, float* f) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void qkn_store4(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+__device__ __forceinline__ void qkn_store4(bf16* p, const float* f) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 r;
+  r.x = *reinterpret_cast<uint32_t*>(&a);
+  r.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = r;
+}
+
+// VEC: rows are read and written four elements at a time (d and dv multiples of 4, aligned pointers and strides).
+template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(QKN_WARPS * 32)
 qk_norm_rope_write_kernel(const TI* q, long q_stride, const TI* k, long k_stride, const TI* v, long v_stride,
                           TO* q_out, long qo_stride, const void* __restrict__ q_w, const void* __restrict__ k_w,
@@ -51,13 +69,26 @@ qk_norm_rope_write_kernel(const TI* q, long q_stride, const TI* k, long k_stride
     if (slot >= 0) {
       const TI* vr = v + (size_t)t * v_stride + (size_t)h * dv;
       TO* dst = v_cache + page_at * dv;
-      for (int i = lane; i < dv; i += 32) dst[i] = from_f32<TO>(to_f32(vr[i]));
+      if (VEC) {
+        for (int i = lane * 4; i < dv; i += 128) { float f[4]; qkn_load4(vr + i, f); qkn_store4(dst + i, f); }
+      } else {
+        for (int i = lane; i < dv; i += 32) dst[i] = from_f32<TO>(to_f32(vr[i]));
+      }
     }
     return;
   }
   const TI* row = (which == 0 ? q + (size_t)t * q_stride : k + (size_t)t * k_stride) + (size_t)h * d;
   float ss = 0.f;
-  for (int i = lane; i < d; i += 32) { const float x = to_f32(row[i]); xs[i] = x; ss += x * x; }
+  if (VEC) {
+    for (int i = lane * 4; i < d; i += 128) {
+      float f[4];
+      qkn_load4(row + i, f);
+      *reinterpret_cast<float4*>(xs + i) = make_float4(f[0], f[1], f[2], f[3]);
+      ss += (f[0] * f[0] + f[1] * f[1]) + (f[2] * f[2] + f[3] * f[3]);
+    }
+  } else {
+    for (int i = lane; i < d; i += 32) { const float x = to_f32(row[i]); xs[i] = x; ss += x * x; }
+  }
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)d + eps);
   const void* w = which == 0 ? q_w : k_w;
@@ -77,12 +108,15 @@ qk_norm_rope_write_kernel(const TI* q, long q_stride, const TI* k, long k_stride
     }
     __syncwarp();
   }
-  if (which == 0) {
-    TO* dst = q_out + (size_t)t * qo_stride + (size_t)h * d;
-    for (int i = lane; i < d; i += 32) dst[i] = from_f32<TO>(xs[i]);
-  } else if (slot >= 0) {
-    TO* dst = k_cache + page_at * d;
-    for (int i = lane; i < d; i += 32) dst[i] = from_f32<TO>(xs[i]);
+  TO* dst = nullptr;
+  if (which == 0) dst = q_out + (size_t)t * qo_stride + (size_t)h * d;
+  else if (slot >= 0) dst = k_cache + page_at * d;
+  if (dst != nullptr) {
+    if (VEC) {
+      for (int i = lane * 4; i < d; i += 128) qkn_store4(dst + i, xs + i);
+    } else {
+      for (int i = lane; i < d; i += 32) dst[i] = from_f32<TO>(xs[i]);
+    }
   }
 }
 
@@ -106,12 +140,17 @@ PHOTON_API int photon_qk_norm_rope_write(const void* q, long q_stride, const voi
   dim3 grid((items + QKN_WARPS - 1) / QKN_WARPS, T);
   const size_t smem = (size_t)QKN_WARPS * d * sizeof(float);
   const int wb = (w_dtype == PHOTON_BF16);
-#define QKN_LAUNCH(TI, TO) do { \
-    if (smem > 48 * 1024) { cudaError_t e_ = cudaFuncSetAttribute(qk_norm_rope_write_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+  const uintptr_t ia = in_dtype == PHOTON_F32 ? 16 : 8, oa = out_dtype == PHOTON_F32 ? 16 : 8;   // bytes of four elements
+  const bool vec = d % 4 == 0 && dv % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 && qo_stride % 4 == 0 &&
+                   (uintptr_t)q % ia == 0 && (uintptr_t)k % ia == 0 && (uintptr_t)v % ia == 0 && (uintptr_t)q_out % oa == 0 &&
+                   (uintptr_t)k_cache % oa == 0 && (uintptr_t)v_cache % oa == 0;
+#define QKN_GO(TI, TO, VEC) do { \
+    if (smem > 48 * 1024) { cudaError_t e_ = cudaFuncSetAttribute(qk_norm_rope_write_kernel<TI, TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
                             if (e_ != cudaSuccess) return (int)e_; } \
-    return launch_pdl(qk_norm_rope_write_kernel<TI, TO>, grid, dim3(QKN_WARPS * 32), smem, stream, (const TI*)q, q_stride, \
+    return launch_pdl(qk_norm_rope_write_kernel<TI, TO, VEC>, grid, dim3(QKN_WARPS * 32), smem, stream, (const TI*)q, q_stride, \
         (const TI*)k, k_stride, (const TI*)v, v_stride, (TO*)q_out, qo_stride, q_w, k_w, wb, eps, positions, inv_freq, rot_dims, \
         slot_mapping, (TO*)k_cache, (TO*)v_cache, n_q, n_kv, d, dv, page_size, num_slots, err); } while (0)
+#define QKN_LAUNCH(TI, TO) do { if (vec) QKN_GO(TI, TO, true); else QKN_GO(TI, TO, false); } while (0)
   if (in_dtype == PHOTON_F32 && out_dtype == PHOTON_F32) QKN_LAUNCH(float, float);
   if (in_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16) QKN_LAUNCH(float, bf16);
   if (in_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16) QKN_LAUNCH(bf16, bf16);

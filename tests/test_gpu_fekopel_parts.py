@@ -243,7 +243,7 @@ LENGTHS, COUNTS = [33, 150, 97, 200, 1, 300], [33, 50, 1, 2, 1, 1]
 
 
 @pytest.mark.parametrize("rule", RULES, ids=lambda r: f"w{r['window']}k{r['keep']}s{int(r['sink'])}c{r['cap']}")
-@pytest.mark.parametrize("heads", [(2, 1), (4, 2), (2, 2), (8, 1)])
+@pytest.mark.parametrize("heads", [(2, 1), (6, 2), (2, 2), (8, 1), (5, 1)])
 @pytest.mark.parametrize("kernel,dtype,d,dv,page", [("general", torch.float32, 10, 14, 8), ("general", torch.float32, 64, 64, 16),
                                                     ("general", torch.bfloat16, 24, 8, 16), ("tensor", torch.bfloat16, 64, 64, 16),
                                                     ("tensor", torch.bfloat16, 128, 128, 16), ("tensor", torch.bfloat16, 64, 64, 64),
