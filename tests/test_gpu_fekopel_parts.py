@@ -415,3 +415,30 @@ def test_plain_experts_on_every_path(dtype, rows, shape):
     else:
         # bfloat16 products of bfloat16 inputs agree with the oracle on the experts (the router sees the same numbers)
         assert float(per_row.max()) < 2.5e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [5, 70, 400])
+def test_experts_that_nobody_chooses(dtype, rows):
+    """Two of eight experts never win (their router rows point away from every input): their groups of rows are
+    empty on every path, and the others' results do not move."""
+    from photon_infer_b200.models.fekopel import _feed_forward
+    from photon_infer_b200.parts.registry import create_part
+    H = 64
+    m = dict(kind="moe", router=dict(experts=8, top=1, scale=1.0), expert=dict(ff=32))
+    spec = _feed_forward(types.SimpleNamespace(width=H), m)
+    ff = create_part("feed_forward", spec.kind, spec.params)
+    g = torch.Generator().manual_seed(21)
+    w = {t.name: (0.3 * torch.randn(t.concrete_shape(), generator=g)) for t in ff.tensor_specs()}
+    w["router"][:, 0] = 2.0
+    w["router"][3, 0] = w["router"][5, 0] = -2.0
+    w = {k: v.to(dtype) for k, v in w.items()}
+    ff.load({k: v.to(DEV) for k, v in w.items()})
+    h = torch.randn(rows, H, generator=g)
+    h[:, 0] = 5.0
+    h = h.to(dtype)
+    wd = {k: v.double() for k, v in w.items()}
+    ids, _ = plain.route(h.double(), m, wd)
+    assert not ((ids == 3) | (ids == 5)).any()
+    got = ff.forward(h.to(DEV), None).float().cpu()
+    assert rel_err(got, plain.moe(h.double(), m, wd)) < (1e-5 if dtype == torch.float32 else 2.5e-2)
