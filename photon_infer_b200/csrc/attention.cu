@@ -35,7 +35,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const int* __restrict__ token_seq, const int* __restrict__ positions,
                        int n_q, int n_kv, int d, int dv, int hb, int page_size, int num_pages, int window,
                        float scale, int splits, float* __restrict__ part, int* err, int keep_first, int sink,
-                       float softcap) {
+                       float softcap, const T* __restrict__ gate, long gate_stride) {
   extern __shared__ __align__(16) float smem[];
   const int chunks = (n_q / n_kv + hb - 1) / hb;
   const int t = blockIdx.x, g = blockIdx.y / chunks;
@@ -194,7 +194,9 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
         dst[j] = acc[n];
         if (j == 0) { dst[dv] = mrun[h]; dst[dv + 1] = l; }
       } else {
-        out[(size_t)t * out_stride + (size_t)(h0 + h) * dv + j] = from_f32<T>(l > 0.f ? acc[n] / l : 0.f);
+        float y = l > 0.f ? acc[n] / l : 0.f;
+        if (gate) y = y / (1.0f + expf(-to_f32(gate[(size_t)t * gate_stride + (size_t)(h0 + h) * dv + j])));
+        out[(size_t)t * out_stride + (size_t)(h0 + h) * dv + j] = from_f32<T>(y);
       }
     }
   }
@@ -203,7 +205,7 @@ paged_attention_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
 // The shares of one (token, head) put together, in the order of the shares.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part, int splits, int dv, T* __restrict__ out,
-                                       long out_stride, int n_q, int sink) {
+                                       long out_stride, int n_q, int sink, const T* __restrict__ gate, long gate_stride) {
   const int t = blockIdx.x, h = blockIdx.y;
   const float* src = part + ((size_t)t * n_q + h) * splits * (dv + 2);
   float m = -INFINITY;
@@ -220,7 +222,9 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int split
       const float ms = src[s * (dv + 2) + dv];
       if (ms != -INFINITY) a += src[s * (dv + 2) + j] * expf(ms - m);
     }
-    out[(size_t)t * out_stride + (size_t)h * dv + j] = from_f32<T>(l > 0.f ? a / l : 0.f);
+    float y = l > 0.f ? a / l : 0.f;
+    if (gate) y = y / (1.0f + expf(-to_f32(gate[(size_t)t * gate_stride + (size_t)h * dv + j])));
+    out[(size_t)t * out_stride + (size_t)h * dv + j] = from_f32<T>(y);
   }
 }
 
@@ -229,7 +233,8 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
                             const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                             const int* positions, int T_, int n_q, int n_kv, int d, int dv, int hb, int page_size,
                             int num_pages, int window, float scale, int splits, float* part, int* err,
-                            cudaStream_t stream, int keep_first, int sink, float softcap) {
+                            cudaStream_t stream, int keep_first, int sink, float softcap, const void* gate,
+                            long gate_stride) {
   const int G = hb;
   const size_t floats = (size_t)G * d + ATT_TILE * (d + 1) + (v_cache == k_cache ? 0 : ATT_TILE * dv) +
                         (size_t)G * ATT_TILE + 3 * G + 1;
@@ -244,10 +249,10 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
   paged_attention_kernel<T, PPT><<<grid, ATT_THREADS, smem, stream>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_table,
       max_pages, token_seq, positions, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err,
-      keep_first, sink, softcap);
+      keep_first, sink, softcap, splits > 1 ? nullptr : (const T*)gate, gate_stride);
   int st = launch_status();
   if (st != 0 || splits <= 1) return st;
-  attention_merge_kernel<T><<<dim3(T_, n_q), 128, 0, stream>>>(part, splits, dv, (T*)out, out_stride, n_q, sink);
+  attention_merge_kernel<T><<<dim3(T_, n_q), 128, 0, stream>>>(part, splits, dv, (T*)out, out_stride, n_q, sink, (const T*)gate, gate_stride);
   return launch_status();
 }
 
@@ -262,7 +267,7 @@ static int attention_launch(const void* q, long q_stride, void* out, long out_st
 
 #define ATT_ARGS q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, token_seq, \
                  positions, T_, n_q, n_kv, d, dv, hb, page_size, num_pages, window, scale, splits, part, err, stream, \
-                 keep_first, sink, softcap
+                 keep_first, sink, softcap, gate, gate_stride
 
 // window <= 0: all keys.  Strides in elements.  The key cache holds [num_pages][n_kv][page_size][d], the value
 // cache [num_pages][n_kv][page_size][dv]; v_cache == k_cache (dv <= d): a key's value is the head of its row.
@@ -277,19 +282,20 @@ PHOTON_API int photon_paged_attention(const void* q, long q_stride, void* out, l
                                       float scale, int splits, float* part, int* err, cudaStream_t stream) {
   return photon_paged_attention_ex(q, q_stride, out, out_stride, dtype, k_cache, v_cache, block_table, max_pages, token_seq,
                                    positions, T_, n_q, n_kv, d, dv, page_size, num_pages, window, scale, splits, part, err,
-                                   0, 0, 0.f, stream);
+                                   0, 0, 0.f, nullptr, 0, stream);
 }
 
 // The same with three more rules.  keep_first > 0 (with a window): keys 0 .. keep_first - 1 stay visible behind the
 // window, at their true positions.  sink != 0: the softmax has one more key with score 0 and no value, so the
 // weights of a row add up to less than one: p_j = exp(s_j) / (exp(0) + sum exp(s_i)).  softcap > 0: scores are
-// bounded, s <- softcap * tanh(s / softcap), after the scale.
+// bounded, s <- softcap * tanh(s / softcap), after the scale.  gate (may be null; the type of q, [T][n_q * dv] with row
+// stride gate_stride): every output is multiplied by sigmoid(gate) before it is rounded.
 PHOTON_API int photon_paged_attention_ex(const void* q, long q_stride, void* out, long out_stride, int dtype,
                                          const void* k_cache, const void* v_cache, const int* block_table,
                                          int max_pages, const int* token_seq, const int* positions, int T_,
                                          int n_q, int n_kv, int d, int dv, int page_size, int num_pages, int window,
                                          float scale, int splits, float* part, int* err, int keep_first, int sink,
-                                         float softcap, cudaStream_t stream) {
+                                         float softcap, const void* gate, long gate_stride, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (splits < 1 || splits > 64 || (splits > 1 && part == nullptr) || T_ > 65535 * 32) return PHOTON_ERR_ARGUMENT;

@@ -94,6 +94,7 @@ struct FlashParams {
   // softcap * tanh(score * scale / softcap); cap_in = scale / softcap.
   int keep_first, sink;
   float softcap, cap_in;
+  const bf16* gate; long gate_stride;     // may be null: [T, n_q * d]; every output is multiplied by sigmoid(gate)
 };
 
 // tanh through one exponential and one reciprocal: 1 - 2 / (2^(2 x log2 e) + 1); absolute error about 1e-7.
@@ -405,9 +406,16 @@ flash_attention_kernel(const FlashParams P) {
       if (P.sink) l[h2] += exp2f(-m[h2]);                                   // the sink's weight, relative to the running maximum
       const float inv = l[h2] > 0.f ? 1.f / l[h2] : 0.f;
       bf16* dst = P.out + (size_t)(tok0 + tk) * P.out_stride + (size_t)(g * G + h) * HEAD_DIM + (lane & 3) * 2;
+      const bf16* gt = P.gate ? P.gate + (size_t)(tok0 + tk) * P.gate_stride + (size_t)(g * G + h) * HEAD_DIM + (lane & 3) * 2 : nullptr;
 #pragma unroll
-      for (int n = 0; n < FA_ND; ++n)
-        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][h2 * 2] * inv, o[n][h2 * 2 + 1] * inv);
+      for (int n = 0; n < FA_ND; ++n) {
+        float y0 = o[n][h2 * 2] * inv, y1 = o[n][h2 * 2 + 1] * inv;
+        if (gt) {
+          const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gt + n * 8));
+          y0 = __fdividef(y0, 1.0f + __expf(-z.x)); y1 = __fdividef(y1, 1.0f + __expf(-z.y));
+        }
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(y0, y1);
+      }
     }
     return;
   }
@@ -449,7 +457,9 @@ flash_attention_kernel(const FlashParams P) {
     const int head = g * G + h;
     if (P.num_splits == 1) {
       if (P.sink && M != -INFINITY) L += exp2f(-M);
-      P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+      float y = L > 0.f ? A / L : 0.f;
+      if (P.gate) y = __fdividef(y, 1.0f + __expf(-__bfloat162float(P.gate[(size_t)(tok0 + tk) * P.gate_stride + (size_t)head * HEAD_DIM + d])));
+      P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(y);
     } else {
       const size_t slot = ((size_t)(tok0 + tk) * n_q + head) * P.num_splits + split;
       __stcg(P.part_acc + slot * HEAD_DIM + d, A);
@@ -482,7 +492,9 @@ flash_attention_kernel(const FlashParams P) {
       }
       if (P.sink) L += exp2f(-M);
     }
-    P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+    float y = L > 0.f ? A / L : 0.f;
+    if (P.gate) y = __fdividef(y, 1.0f + __expf(-__bfloat162float(P.gate[(size_t)(tok0 + tk) * P.gate_stride + (size_t)head * HEAD_DIM + d])));
+    P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(y);
   }
 }
 
@@ -510,11 +522,13 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
                                       int nsub, int mode, int* err, cudaStream_t stream) {
   return photon_flash_attention_ex(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, cu_tokens, positions,
                                    context_lens, part_acc, part_ml, tickets, S, max_tokens_per_seq, n_q, n_kv, d, page_size,
-                                   num_pages, window, scale, num_splits, nsub, mode, err, 0, 0, 0.f, stream);
+                                   num_pages, window, scale, num_splits, nsub, mode, err, 0, 0, 0.f, nullptr, 0, stream);
 }
 
 // The same with kept first keys (with a window, keys 0 .. keep_first - 1 stay visible behind it), a sink (one more
 // key with score 0 and no value in the softmax) and bounded scores (softcap * tanh(score * scale / softcap); 0: off).
+// gate (may be null): bfloat16 [T, n_q * d] with row stride gate_stride (a multiple of 2, 4-byte aligned rows); every
+// output is multiplied by sigmoid(gate) before it is rounded.
 PHOTON_API int photon_flash_attention_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                          const void* v_cache, const int* block_table, int max_pages,
                                          const int* cu_tokens, const int* positions, const int* context_lens,
@@ -522,7 +536,7 @@ PHOTON_API int photon_flash_attention_ex(const void* q, long q_stride, void* out
                                          int* tickets, int S, int max_tokens_per_seq, int n_q, int n_kv, int d,
                                          int page_size, int num_pages, int window, float scale, int num_splits,
                                          int nsub, int mode, int* err, int keep_first, int sink, float softcap,
-                                         cudaStream_t stream) {
+                                         const void* gate, long gate_stride, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
@@ -542,6 +556,8 @@ PHOTON_API int photon_flash_attention_ex(const void* q, long q_stride, void* out
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   P.keep_first = window > 0 ? keep_first : 0; P.sink = sink; P.softcap = softcap; P.cap_in = 0.f;
   if (softcap > 0.f) { P.cap_in = scale / softcap; P.scale_log2 = 1.4426950408889634f; }
+  if (gate != nullptr && (((uintptr_t)gate & 3) || (gate_stride & 1))) return PHOTON_ERR_ARGUMENT;
+  P.gate = (const bf16*)gate; P.gate_stride = gate_stride;
   const size_t ring = (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD;
   const size_t ring2 = (size_t)2 * 2 * FA_TILE_K * FA_LD;                   // two stages
   const size_t smem_rows = ((size_t)FA_ROWS * FA_LD + ring) * sizeof(bf16);

@@ -85,6 +85,7 @@ struct AttnTcParams {
   // value in the softmax.  softcap > 0: scores become softcap * tanh(score * cap_in), cap_in = scale / softcap.
   int keep_first, sink;
   float softcap, cap_in;
+  const bf16* gate; long gate_stride;              // may be null: [T, n_q * d]; every output is multiplied by sigmoid(gate)
 };
 
 // D += A B with A in tensor memory (128 lanes x 8 columns of packed bfloat16 pairs per 16 of K), B in shared memory.
@@ -402,6 +403,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int tk = valid ? row / G : 0, h = valid ? row - tk * G : 0;
       bf16* dst = P.out + (size_t)(tok0 + tk) * P.out_stride + (size_t)(g * G + h) * HEAD_DIM;
+      const bf16* gt = P.gate ? P.gate + (size_t)(tok0 + tk) * P.gate_stride + (size_t)(g * G + h) * HEAD_DIM : nullptr;
 #pragma unroll 1
       for (int cc = 0; cc < HEAD_DIM; cc += 32) {
         uint32_t ov[32];
@@ -409,6 +411,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (valid) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
+            if (gt) {
+              // eight gates of this row (16 bytes): the output times sigmoid(gate), folded into the numbers before `inv`
+              const uint4 gz = *reinterpret_cast<const uint4*>(gt + cc + j);
+              const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gz);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 z = __bfloat1622float2(gp[u]);
+                ov[j + 2 * u] = __float_as_uint(__fdividef(__uint_as_float(ov[j + 2 * u]), 1.0f + __expf(-z.x)));
+                ov[j + 2 * u + 1] = __float_as_uint(__fdividef(__uint_as_float(ov[j + 2 * u + 1]), 1.0f + __expf(-z.y)));
+              }
+            }
             uint4 v4;
             v4.x = at_pack(__uint_as_float(ov[j]) * inv, __uint_as_float(ov[j + 1]) * inv);
             v4.y = at_pack(__uint_as_float(ov[j + 2]) * inv, __uint_as_float(ov[j + 3]) * inv);
@@ -443,15 +456,16 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
                                    cudaStream_t stream) {
   return photon_attention_tc_ex(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_pages, cu_tokens, positions,
                                 S, max_tokens_per_seq, T, n_q, n_kv, d, page_size, num_pages, window, scale, err, 0, 0, 0.f,
-                                stream);
+                                nullptr, 0, stream);
 }
 
-// The same with kept first keys, a sink and bounded scores (see AttnTcParams).
+// The same with kept first keys, a sink and bounded scores (see AttnTcParams), and an optional gate: bfloat16
+// [T, n_q * d] with row stride gate_stride (16-byte aligned rows); every output is multiplied by sigmoid(gate).
 PHOTON_API int photon_attention_tc_ex(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                       const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
                                       const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
                                       int page_size, int num_pages, int window, float scale, int* err, int keep_first,
-                                      int sink, float softcap, cudaStream_t stream) {
+                                      int sink, float softcap, const void* gate, long gate_stride, cudaStream_t stream) {
   if (S <= 0 || T <= 0) return 0;
   if (keep_first < 0 || softcap < 0.f) return PHOTON_ERR_ARGUMENT;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
@@ -489,6 +503,8 @@ PHOTON_API int photon_attention_tc_ex(const void* q, long q_stride, void* out, l
   P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   P.keep_first = window > 0 ? keep_first : 0; P.sink = sink; P.softcap = softcap; P.cap_in = 0.f;
   if (softcap > 0.f) { P.cap_in = scale / softcap; P.scale_log2 = 1.4426950408889634f; }
+  if (gate != nullptr && (((uintptr_t)gate & 15) || (gate_stride & 7))) return PHOTON_ERR_ARGUMENT;
+  P.gate = (const bf16*)gate; P.gate_stride = gate_stride;
   const long rows = (long)max_tokens_per_seq * G;
   P.tiles_per_seq = (int)((rows + P.tile_rows - 1) / P.tile_rows);
   if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;

@@ -117,12 +117,14 @@ PHOTON_EXPORT int photon_paged_attention(const void* q, long q_stride, void* out
                            const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
                            int window, float scale, int splits, float* part, int* err, cudaStream_t stream);
 /* The same with kept first keys (keys < keep_first stay visible behind the window), a sink (one more key with score 0 and
- * no value in the softmax's denominator) and bounded scores (s <- softcap * tanh(s / softcap); 0: off). */
+ * no value in the softmax's denominator) and bounded scores (s <- softcap * tanh(s / softcap); 0: off).  gate (may be
+ * null; here and in the two tensor-core kernels below): [T, n_q * dv] of the type of q, row stride gate_stride; every
+ * output is multiplied by sigmoid(gate) before it is rounded. */
 PHOTON_EXPORT int photon_paged_attention_ex(const void* q, long q_stride, void* out, long out_stride, int dtype, const void* k_cache,
                               const void* v_cache, const int* block_table, int max_pages, const int* token_seq,
                               const int* positions, int T_, int n_q, int n_kv, int d, int dv, int page_size, int num_pages,
                               int window, float scale, int splits, float* part, int* err, int keep_first, int sink,
-                              float softcap, cudaStream_t stream);
+                              float softcap, const void* gate, long gate_stride, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ latent.cu: attention over a cached latent */
 /* One pass over a token's fused down-projection row down[t] = [query latent (q_rank) | key/value latent (kv_rank) |
@@ -232,7 +234,7 @@ PHOTON_EXPORT int photon_flash_attention_ex(const void* q, long q_stride, void* 
                               const int* positions, const int* context_lens, float* part_acc, float* part_ml, int* tickets,
                               int S, int max_tokens_per_seq, int n_q, int n_kv, int d, int page_size, int num_pages,
                               int window, float scale, int num_splits, int nsub, int mode, int* err, int keep_first,
-                              int sink, float softcap, cudaStream_t stream);
+                              int sink, float softcap, const void* gate, long gate_stride, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_tc.cu (-DHEAD_DIM=64|128; bfloat16; tcgen05) */
 PHOTON_EXPORT int photon_attention_tc_head_dim(void);
@@ -245,7 +247,7 @@ PHOTON_EXPORT int photon_attention_tc_ex(const void* q, long q_stride, void* out
                            const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
                            const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
                            int page_size, int num_pages, int window, float scale, int* err, int keep_first, int sink,
-                           float softcap, cudaStream_t stream);
+                           float softcap, const void* gate, long gate_stride, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ attention_decode.cu (-DHEAD_DIM=64|128; bfloat16; TMA) */
 PHOTON_EXPORT int photon_attention_decode_head_dim(void);

@@ -368,11 +368,25 @@ def qk_norm_rope_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[t
 
 # ----------------------------------------------------------------------------- attention
 
+def _check_gate(gate: Optional[torch.Tensor], q: torch.Tensor, out: torch.Tensor) -> None:
+    if gate is None:
+        return
+    _cuda(gate)
+    if gate.shape != out.shape or gate.stride(1) != 1 or gate.dtype != q.dtype:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention: the gate must have the shape of the output and the type of q")
+
+
+def gate_fusable(gate: torch.Tensor) -> bool:
+    """Whether the tensor-core attention kernels can take this gate into their epilogue (16-byte aligned rows)."""
+    return gate.stride(1) == 1 and gate.data_ptr() % 16 == 0 and (gate.stride(0) * gate.element_size()) % 16 == 0
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float,
                     err: Optional[torch.Tensor], value_dim: Optional[int] = None, splits: int = 1,
-                    keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None) -> None:
+                    keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None,
+                    gate: Optional[torch.Tensor] = None) -> None:
     """General paged causal attention.  ``q`` is a ``[T, n_q * d]`` view (row stride free),
     ``out [T, n_q * dv]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
     ``max(0, p - window + 1) .. p`` through ``block_table[seq]``.  ``value_dim`` (default ``head_dim``) is the
@@ -381,7 +395,9 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     blocks (for decoded tokens with long contexts; the order of the sums then depends on ``splits``).
     ``keep_first``: with a window, keys ``0 .. keep_first - 1`` stay visible as well.  ``sink``: the softmax has one
     more key with score 0 and no value (``p_j = exp(s_j) / (1 + sum exp(s_i))``).  ``softcap``: scores become
-    ``softcap * tanh(score / softcap)`` after the scale."""
+    ``softcap * tanh(score / softcap)`` after the scale.  ``gate`` (``[T, n_q * value_dim]`` of the type of ``q``, a
+    view with any row stride): every output is multiplied by ``sigmoid(gate)`` before it is rounded."""
+    _check_gate(gate, q, out)
     _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
     T = q.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
@@ -400,13 +416,14 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     f = _fn("attention", "photon_paged_attention_ex",
             [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int,
-             c_float, c_void_p])
+             c_float, c_void_p, c_long, c_void_p])
     splits = max(1, min(int(splits), 64))
     part = torch.empty(T * n_q * splits * (dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
              _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim, dv,
              k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), splits, _ptr(part), _ptr(err),
-             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "paged_attention")
+             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             _stream()), "paged_attention")
     if splits > 1:
         global _launch_count
         _launch_count += 1
@@ -450,7 +467,7 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
                     window: Optional[int], scale: float, num_splits: int, scratch: Optional[torch.Tensor],
                     rows_mode: bool, keys_mode: bool, err: Optional[torch.Tensor],
                     context_lens: Optional[torch.Tensor] = None, key_groups: int = 1, keep_first: int = 0,
-                    sink: bool = False, softcap: Optional[float] = None) -> None:
+                    sink: bool = False, softcap: Optional[float] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention on the tensor cores.  ``cu_tokens [S + 1]`` gives each request's
     tokens in the step.  ``rows_mode``: run requests with more than 16 rows (tokens x heads per
     group); ``keys_mode``: run the others, their keys split over ``num_splits`` blocks.
@@ -460,7 +477,8 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     ``key_groups``: 1, 2 or 4 groups of four warps per block of the split-key kernel, each walking its own
     share of the block's keys (``flash_attention_max_groups`` bounds it); their results are merged in shared
     memory, which is far cheaper than the merge of ``num_splits`` blocks through global memory.
-    ``keep_first``, ``sink``, ``softcap``: as in ``paged_attention``."""
+    ``keep_first``, ``sink``, ``softcap``, ``gate``: as in ``paged_attention``."""
+    _check_gate(gate, q, out)
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, scratch, err, context_lens)
     if context_lens is not None:
         _int32(context_lens, "context_lens")
@@ -492,14 +510,15 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     f = _fn("attention_flash", "photon_flash_attention_ex",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-             c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+             c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_long, c_void_p],
             defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
              block_table.shape[1], _ptr(cu_tokens), _ptr(positions), _ptr(context_lens), _ptr(part_acc), _ptr(part_ml),
              _ptr(tickets),
              int(num_seqs), int(max_tokens_per_seq), n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0],
              int(window) if window else 0, float(scale), splits, int(key_groups) if keys_mode else 1, mode, _ptr(err),
-             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "flash_attention")
+             int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             _stream()), "flash_attention")
     if rows_mode and keys_mode:
         global _launch_count
         _launch_count += 1
@@ -624,11 +643,12 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
                  block_table: torch.Tensor, cu_tokens: torch.Tensor, positions: torch.Tensor,
                  num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
                  window: Optional[int], scale: float, err: Optional[torch.Tensor], keep_first: int = 0,
-                 sink: bool = False, softcap: Optional[float] = None) -> None:
+                 sink: bool = False, softcap: Optional[float] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention of the requests that bring more than 16 rows (tokens x heads per
     group) in this step, on the tcgen05 tensor cores; the rows of the other requests are left
-    untouched (``flash_attention`` with ``keys_mode`` takes them).  ``keep_first``, ``sink``, ``softcap``: as in
-    ``paged_attention``."""
+    untouched (``flash_attention`` with ``keys_mode`` takes them).  ``keep_first``, ``sink``, ``softcap``, ``gate``: as in
+    ``paged_attention`` (the gate's rows must start on 16-byte boundaries: ``gate_fusable``)."""
+    _check_gate(gate, q, out)
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, err)
     T = q.shape[0]
     if n_kv <= 0 or n_q % n_kv or not attention_tc_supported(q.dtype, head_dim, n_q // n_kv, k_cache.shape[2]):
@@ -647,12 +667,13 @@ def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_ca
     f = _fn("attention_tc", "photon_attention_tc_ex",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_float,
-             c_void_p],
+             c_void_p, c_long, c_void_p],
             defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
              block_table.shape[1], _ptr(cu_tokens), _ptr(positions), int(num_seqs), int(max_tokens_per_seq), T,
              n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale),
-             _ptr(err), int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _stream()), "attention_tc")
+             _ptr(err), int(keep_first or 0), int(bool(sink)), float(softcap or 0.0), _ptr(gate),
+             gate.stride(0) if gate is not None else 0, _stream()), "attention_tc")
 
 
 # ----------------------------------------------------------------------------- matrix products

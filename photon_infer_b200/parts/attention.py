@@ -156,14 +156,15 @@ class PagedAttention(Mixer):
 
 
 def attend_tensor_cores(mixer, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache,
-                        keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None) -> None:
+                        keep_first: int = 0, sink: bool = False, softcap: Optional[float] = None,
+                        gate: Optional[torch.Tensor] = None) -> None:
     """The tensor-core attention kernels for one step of ``mixer`` (anything with ``n_q``, ``n_kv``, ``head_dim``,
     ``window``, ``scale`` and a ``_max_groups`` slot): requests with many rows walk their keys in one block per 128
     rows, requests with few rows (decoded tokens) split their keys over blocks.  ``keep_first``, ``sink``,
-    ``softcap``: the rules of ``ops.paged_attention``; the persistent kernel for long contexts has none of them."""
+    ``softcap``, ``gate``: the rules of ``ops.paged_attention``; the persistent kernel for long contexts has none of them."""
     self = mixer
-    extras = dict(keep_first=keep_first, sink=sink, softcap=softcap)
-    plain = not (keep_first or sink or softcap)
+    extras = dict(keep_first=keep_first, sink=sink, softcap=softcap, gate=gate)
+    plain = not (keep_first or sink or softcap) and gate is None
     group = ctx.groups[cache.group]
     gsize = self.n_q // self.n_kv
     # tensor cores: requests with many rows walk their keys in one block per 128 rows, requests

@@ -10,7 +10,7 @@ The heads' outputs may be multiplied by ``sigmoid(W_g h)`` (``h`` the mixer's in
 A value may have another width than a key.
 
 Kernels of a step: ONE product for q, k, v (and the gate); one pass that norms and rotates in 32-bit (angles in
-64-bit) and writes queries, keys and values (``qk_norm.cu``); attention; the gate; the output product.  Prompt portions, decoded tokens and mixed batches take the same path.
+64-bit) and writes queries, keys and values (``qk_norm.cu``); attention, with the gate in its epilogue; the output product.  Prompt portions, decoded tokens and mixed batches take the same path.
 """
 from __future__ import annotations
 
@@ -124,18 +124,23 @@ class NormedAttention(Mixer):
                                cache.k if store else None, cache.v if store else None, self.n_q, self.n_kv, self.head_dim,
                                self.value_dim, ctx.error_flag)
         attn = torch.empty((T, self.n_q * self.value_dim), dtype=h.dtype, device=h.device)
-        self.attend(q, attn, ctx, cache)
-        if self.output_gate:
-            ops.gate_mul(attn, rows[:, nq + nk + nv:])
+        gate = rows[:, nq + nk + nv:] if self.output_gate else None
+        # the gate rides in the epilogue of the attention kernel; a gate whose rows are not 16-byte aligned gets a pass of its own
+        fused = gate is not None and (not self._flash_ok(q.dtype) or ops.gate_fusable(gate))
+        self.attend(q, attn, ctx, cache, gate if fused else None)
+        if gate is not None and not fused:
+            ops.gate_mul(attn, gate)
         return project(attn, self.w_o)
 
-    def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+    def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache,
+               gate: Optional[torch.Tensor] = None) -> None:
         """bfloat16 with heads the tensor-core kernels are compiled for (keys and values of one width): those
         kernels, tcgen05 for prompt portions and the split-key kernel for decoded tokens.  float32 and other sizes:
         the general kernel, whose sums depend on a token's position alone; its bfloat16 decode steps share a
         token's keys out over blocks."""
         if self._flash_ok(q.dtype):
-            attend_tensor_cores(self, q, out, ctx, cache, keep_first=self.keep_first, sink=self.sink, softcap=self.softcap)
+            attend_tensor_cores(self, q, out, ctx, cache, keep_first=self.keep_first, sink=self.sink, softcap=self.softcap,
+                                gate=gate)
             return
         group = ctx.groups[cache.group]
         splits = 1
@@ -145,7 +150,7 @@ class NormedAttention(Mixer):
             splits = max(1, min(keys // 128, (2 * ops.sm_count(q.device)) // blocks, 64))
         ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions, self.n_q, self.n_kv,
                             self.head_dim, self.window, self.scale, ctx.error_flag, value_dim=self.value_dim, splits=splits,
-                            keep_first=self.keep_first, sink=self.sink, softcap=self.softcap)
+                            keep_first=self.keep_first, sink=self.sink, softcap=self.softcap, gate=gate)
 
 
 register_mixer("normed_attention", NormedAttention)

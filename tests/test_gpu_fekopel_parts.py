@@ -215,7 +215,7 @@ class _Step:
         return torch.cat([_oracle(self.q[s].double(), self.k[s].double(), self.v[s].double(), self.pos[s], scale, window, keep,
                                   sink, cap) for s in range(len(self.lengths))])
 
-    def run(self, kernel, scale, window, keep, sink, cap, splits=1):
+    def run(self, kernel, scale, window, keep, sink, cap, splits=1, gate=None):
         from photon_infer_b200.kernels import ops
         from photon_infer_b200.parts.attention import attend_tensor_cores
         from photon_infer_b200.parts.base import LayerCache
@@ -223,12 +223,18 @@ class _Step:
         ctx = self.ctx()
         q = torch.cat(self.q).reshape(-1, nq * d).to(DEV)
         out = torch.full((q.shape[0], nq * dv), float("nan"), dtype=self.dtype, device=DEV)
+        if gate is not None:
+            wide = torch.zeros(q.shape[0], nq * dv + 16, dtype=self.dtype, device=DEV)     # a view with a row stride, 16-byte aligned rows
+            wide[:, 8:8 + nq * dv] = gate.to(DEV)
+            gate = wide[:, 8:8 + nq * dv]
         if kernel == "general":
             ops.paged_attention(q, out, self.kcd, self.vcd, ctx.groups[0].block_table, ctx.token_seq, ctx.positions, nq, nkv, d,
-                                window, scale, ctx.error_flag, value_dim=dv, splits=splits, keep_first=keep, sink=sink, softcap=cap)
+                                window, scale, ctx.error_flag, value_dim=dv, splits=splits, keep_first=keep, sink=sink, softcap=cap,
+                                gate=gate)
         else:
             mixer = types.SimpleNamespace(n_q=nq, n_kv=nkv, head_dim=d, window=window, scale=scale, _max_groups=None)
-            attend_tensor_cores(mixer, q, out, ctx, LayerCache(group=0, k=self.kcd, v=self.vcd), keep_first=keep, sink=sink, softcap=cap)
+            attend_tensor_cores(mixer, q, out, ctx, LayerCache(group=0, k=self.kcd, v=self.vcd), keep_first=keep, sink=sink, softcap=cap,
+                                gate=gate)
         torch.cuda.synchronize()
         assert ctx.error_flag.cpu().tolist()[0] == 0
         return out.float().cpu()
@@ -253,8 +259,12 @@ def test_attention_rules_in_every_kernel(rule, heads, kernel, dtype, d, dv, page
     nq, nkv = heads
     st = _Step(LENGTHS, COUNTS, nq, nkv, d, dv, page, dtype, seed=nq * 100 + d, std=1.0 if d < 64 else 0.5)
     scale = 1.3 / math.sqrt(d)
-    got = st.run("general" if kernel == "general" else "tc", scale, rule["window"], rule["keep"], rule["sink"], rule["cap"])
+    # with bounded scores (the second kind of mixer) the heads' outputs are gated in the kernel's epilogue as well
+    gate = (2.0 * torch.randn(sum(COUNTS), nq * dv, generator=torch.Generator().manual_seed(d))).to(dtype) if rule["cap"] else None
+    got = st.run("general" if kernel == "general" else "tc", scale, rule["window"], rule["keep"], rule["sink"], rule["cap"], gate=gate)
     want = st.want(scale, rule["window"], rule["keep"], rule["sink"], rule["cap"])
+    if gate is not None:
+        want = want * torch.sigmoid(gate.double())
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     per_row = (got.double() - want).abs().amax(dim=1) / float(want.abs().max())
     assert float(per_row.max()) < tol, f"rows off: {(per_row >= tol).nonzero().flatten().tolist()[:10]}, worst {float(per_row.max()):.3g}"
@@ -266,9 +276,12 @@ def test_attention_with_keys_split_over_blocks(rule):
     sink enters the merged denominator once."""
     st = _Step([700, 1, 333, 520], [1, 1, 1, 1], 4, 2, 24, 8, 16, torch.bfloat16, seed=3)
     want = st.want(0.3, rule["window"], rule["keep"], rule["sink"], rule["cap"])
+    gate = (2.0 * torch.randn(4, 4 * 8, generator=torch.Generator().manual_seed(8))).to(torch.bfloat16)
     for splits in (1, 3, 64):
         got = st.run("general", 0.3, rule["window"], rule["keep"], rule["sink"], rule["cap"], splits=splits)
         assert rel_err(got, want) < 2e-2
+        got = st.run("general", 0.3, rule["window"], rule["keep"], rule["sink"], rule["cap"], splits=splits, gate=gate)
+        assert rel_err(got, want * torch.sigmoid(gate.double())) < 2e-2
 
 
 @pytest.mark.parametrize("kernel,dtype,d,page", [("general", torch.float32, 12, 8), ("general", torch.bfloat16, 64, 16),
