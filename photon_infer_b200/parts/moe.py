@@ -22,6 +22,7 @@ over their sum times ``route_scale``.  ``shared_gate``: the shared expert's outp
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -106,20 +107,44 @@ class MoEFeedForward(FeedForward):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = h.shape
         n = T * self.top
+        # A long portion: the shared expert's two products run on a second stream beside the router, the sort, the
+        # gather and the passes between the grouped products, which leave most of the GPU idle.  The weighted sum
+        # waits for them.  Not while a stream is captured, and not for few rows (their products share scratch
+        # memory with others of their kind).
+        shared_done = None
+        if SHARED_EXPERT_STREAM and self.shared_size and n >= GROUPED_LIBRARY_PAIRS and T >= 64 and h.dtype == torch.bfloat16 \
+                and not torch.cuda.is_current_stream_capturing():
+            side = _side_stream(h.device)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                shared_early = self._shared(h)
+                shared_done = torch.cuda.Event()
+                shared_done.record(side)
         routed = ops.moe_route(h, self.w_router, self.b_router, self.top, self.scoring, self.groups, self.keep_groups,
                                self.route_scale, self.w_shared_gate)
         ids, weights, counts = routed[:3]
         sgate = routed[3] if self.w_shared_gate is not None else None
-        shared = self._shared(h) if self.shared_size else None
+        if shared_done is not None:
+            shared = shared_early
+        else:
+            shared = self._shared(h) if self.shared_size else None
         glu, act_name = self.gated, self.activation
         out = torch.empty((T, H), dtype=h.dtype, device=h.device)
+
+        def combine(y, place):
+            if shared_done is not None:
+                torch.cuda.current_stream().wait_event(shared_done)      # the shared expert's rows are there
+            ops.moe_combine(y, place, weights, shared, out, sgate)
+
         if n <= GEMV_MAX_PAIRS and ops.moe_gemv_supported(h, self.w_gate_up) and self.expert_size % 8 == 0:
             # a decode step: nothing is sorted, every pair streams its expert's matrices once
             act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
             ops.moe_gemv(h, self.top, ids, self.w_gate_up, act, glu=glu, activation=act_name)
             y = torch.empty((n, H), dtype=torch.float32, device=h.device)
             ops.moe_gemv(act, 1, ids, self.w_down, y)
-            ops.moe_combine(y, None, weights, shared, out, sgate)
+            combine(y, None)
             return out
         offsets, srt, place, tiles, num_tiles, max_tiles = ops.moe_align(ids, counts)
         if h.dtype == torch.bfloat16 and n >= GROUPED_LIBRARY_PAIRS and H % 8 == 0 and self.expert_size % 8 == 0:
@@ -132,14 +157,26 @@ class MoEFeedForward(FeedForward):
             else:
                 act = ops.activation(gate_up, act_name)
             y = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=offsets[1:])
-            ops.moe_combine(y, place, weights, shared, out, sgate)
+            combine(y, place)
             return out
         act = torch.empty((n, self.expert_size), dtype=h.dtype, device=h.device)
         ops.moe_gemm(h, srt, self.top, self.w_gate_up, act, tiles, num_tiles, max_tiles, glu=glu, activation=act_name)
         y = torch.empty((n, H), dtype=torch.float32, device=h.device)
         ops.moe_gemm(act, None, 1, self.w_down, y, tiles, num_tiles, max_tiles)
-        ops.moe_combine(y, place, weights, shared, out, sgate)
+        combine(y, place)
         return out
+
+
+#: The shared expert of a long portion on a second stream (``PHOTON_MOE_SHARED_STREAM=0``: in line).
+SHARED_EXPERT_STREAM = os.environ.get("PHOTON_MOE_SHARED_STREAM", "1") != "0"
+_side_streams: Dict[tuple, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = (device.type, device.index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 #: Up to this many (token, choice) pairs a bfloat16 step runs one matrix-vector product per pair.
